@@ -5,8 +5,9 @@ of every state tensor.  Cache entries (one per schedule run that writes keys and
 values) with the same need (heads, head size, window) form a *group* with storage and
 a page pool of its own: K and V as [entries][pages][kv_heads][page_tokens][head_dim].
 Position p of a slot lies in page `page_table[slot][p // page_tokens]`, row
-`p % page_tokens`.  A group with a window gives back the pages that have fallen out of
-every future query's window.  Pages are handed out before a step runs and given back
+`p % page_tokens`.  A group with a window (or with chunks) gives back the pages that have
+fallen out of every future query's window (chunk), except those that hold first keys its
+queries keep.  Pages are handed out before a step runs and given back
 when the sequence ends.  Reads are bounded by the length, with one exception: the
 tensor-core prefill attention multiplies the value rows past a sequence's end, in its
 last page, by weights of exactly zero, and 0 * Inf is NaN.  So a page that held another
@@ -38,6 +39,16 @@ class KvNeed:
     head_dim: int
     window: int = 0                     # 0: all keys; w: the last w
     v_head_dim: int = 0                 # the values' head size; 0: the keys'
+    chunk: int = 0                      # c > 0: a query reads only the keys of its own chunk of c positions
+    keep_first: int = 0                 # with a window: the sequence's first n keys stay readable
+
+    def first_needed(self, length: int) -> int:
+        """The lowest position (kept first keys aside) that the next query, at position `length`, can read."""
+        if self.window > 0:
+            return max(0, length - self.window + 1)
+        if self.chunk > 0:
+            return length - length % self.chunk
+        return 0
 
     @property
     def value_dim(self) -> int:
@@ -81,8 +92,9 @@ class KvGroup:
         self.table_host = np.full((n_slots, max_pages), -1, dtype=np.int32)
         self.table_dev = torch.full((n_slots, max_pages), -1, dtype=torch.int32, device=device)
         self._dirty: set[int] = set()
-        self.first_page = [0] * n_slots     # pages below this index were given back (window)
+        self.first_page = [0] * n_slots     # pages below this index were given back (window), bar the kept first ones
         self.held = [0] * n_slots           # pages held from first_page on (they are contiguous)
+        self.kept_pages = -(-need.keep_first // page_tokens) if need.window > 0 else 0   # pages with kept first keys
         self.n_pages = n_pages
         if self.k.is_cuda:
             from ..csrc import ops
@@ -125,20 +137,19 @@ class KvGroup:
 
     def trim(self, slot: int, length: int) -> None:
         """Give back pages that no later query can reach: with a window w the next
-        query, at position `length`, reads keys >= length - w + 1."""
-        w = self.need.window
-        if w <= 0:
-            return
-        keep_from = max(0, length - w + 1) // self.page_tokens
+        query, at position `length`, reads keys >= length - w + 1 (with chunks: from its
+        chunk's start on), and the kept first keys."""
+        keep_from = self.need.first_needed(length) // self.page_tokens
         if keep_from <= self.first_page[slot]:
             return
         row = self.table_host[slot]
         for i in range(self.first_page[slot], keep_from):
             if row[i] >= 0:
-                self.pool.free(int(row[i]))
-                row[i] = -1
-                self.held[slot] -= 1
-                self._dirty.add(slot)
+                self.held[slot] -= 1                    # below first_page now, whether kept or given back
+                if i >= self.kept_pages:
+                    self.pool.free(int(row[i]))
+                    row[i] = -1
+                    self._dirty.add(slot)
         self.first_page[slot] = keep_from
 
     def release(self, slot: int) -> None:
@@ -292,7 +303,7 @@ class SequenceCache:
 
     def commit(self, slots: Sequence[int], n_new: Sequence[int]) -> None:
         """The step has been launched: lengths grow, windows let go of old pages."""
-        windowed = [g for g in self.groups if g.need.window > 0]
+        windowed = [g for g in self.groups if g.need.window > 0 or g.need.chunk > 0]
         for slot, n in zip(slots, n_new):
             self.slots.length[slot] += n
             for g in windowed:

@@ -75,6 +75,17 @@ class PositionSpec:
 
 
 @dataclass(frozen=True)
+class PositionHalfSpec:
+    """Rotary position encoding on the first `rotary_dim` dims of each head, element i paired with element
+    i + rotary_dim / 2, angle position * base^(-2i / rotary_dim); the angles come from a table of `max_positions`
+    rows, and attention fuses the rotation with its cache write."""
+    rotary_dim: int
+    base: float
+    max_positions: int
+    kind: str = "rotary_half_table"
+
+
+@dataclass(frozen=True)
 class AttentionSpec:
     """Causal softmax attention over the sequence's cache.
 
@@ -87,6 +98,13 @@ class AttentionSpec:
     by sigmoid(W_g h) before the output projection.  `value_mix`: "first" keeps the layer's
     values for later layers of the same step, "blend" caches (1 - l) v + l v_first with its
     scalar tensor "value_mix" as l.
+    `chunk` c > 0: a query sees only the keys of its own chunk of c positions, counted from position 0 (no window then).
+    `keep_first` n > 0 with a window: the sequence's first n keys stay visible to every later query.
+    `sink`: a learned number per query head (tensor "sink") whose exponential joins the softmax's denominator without a
+    key or a value.  `maps` = 2 (differential attention): q and k hold two maps per head side by side, each an attention
+    of its own over the same values; with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + `diff` (four vectors of head_dim),
+    o = a1 - lambda a2 per head, divided by its root mean square over the head's values (`eps` inside the root), times
+    (1 - diff).
     """
     width: int
     n_heads: int
@@ -104,6 +122,12 @@ class AttentionSpec:
     softcap: float = 0.0
     gate: bool = False
     value_mix: Optional[str] = None
+    chunk: int = 0
+    keep_first: int = 0
+    sink: bool = False
+    maps: int = 1
+    diff: float = 0.0
+    eps: float = 0.0
 
     @property
     def scale(self) -> float:
@@ -160,16 +184,64 @@ class MlstmSpec:
 class DecayAttentionSpec:
     """Linear attention with a fixed decay per head: S_t = decay_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t, with
     `activation` on q, k and v; the concatenated heads get one RMS norm (plain weight), a sigmoid gate from
-    the mixer's input, and the output projection.  State: [heads, value_dim, key_dim] in 32-bit per sequence."""
+    the mixer's input, and the output projection.  State: [heads, value_dim, key_dim] in 32-bit per sequence.
+    Options: `position` rotates q and k before the recurrence; `key_scale` multiplies k; `norm_per_head` takes each
+    head's root mean square instead of the whole vector's; `norm_weight` False: the norm has no weight;
+    `gate_activation` names the gate's function."""
     width: int
     n_heads: int
     key_dim: int
     value_dim: int
     decay: Tuple[float, ...]
     eps: float
-    activation: str = "silu"
+    activation: Optional[str] = "silu"
     kind: str = "lightning"
     names: Mapping[str, str] = field(default_factory=dict)
+    position: Optional[object] = None
+    key_scale: float = 1.0
+    norm_per_head: bool = False
+    norm_weight: bool = True
+    gate_activation: str = "sigmoid"
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """The gated delta rule.  q, k = W h (`n_qk_heads` heads of key_dim), v = W h (`n_heads` heads of value_dim); each
+    passes a causal convolution over time per channel (`conv_taps` taps, the last the current token's) and silu; q and k
+    become unit vectors per head (x / sqrt(sum x^2 + `unit_eps`)), q times key_dim^-1/2.  Step size beta = sigmoid(W_b h)
+    per head; decay per head and key channel g = exp(-exp(A_log_h) softplus(W_a2 W_a1 h + dt_bias)).  Per head, on
+    S [key_dim, value_dim]: S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.  Each head's o is divided by
+    its root mean square (`eps`), times a weight of value_dim shared by the heads, times sigmoid(W_g2 W_g1 h); then W_o.
+    State per sequence: S in 32-bit and the convolutions' last conv_taps - 1 inputs.  The ranks of the two bottlenecks
+    (-1: whatever the checkpoint holds)."""
+    width: int
+    n_heads: int
+    n_qk_heads: int
+    key_dim: int
+    value_dim: int
+    conv_taps: int
+    eps: float
+    unit_eps: float = 1e-6
+    decay_rank: int = -1
+    gate_rank: int = -1
+    kind: str = "gated_delta"
+    names: Mapping[str, str] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class PairMixerSpec:
+    """Two mixers side by side that read the same input: left_scale * left(h) + right_scale * right(h).  Each keeps its
+    own cache entry (a schedule run names two)."""
+    left: object
+    right: object
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+    kind: str = "pair"
+
+    @property
+    def names(self) -> Mapping[str, str]:
+        """The two mixers' tensors under "left.<name>" and "right.<name>"."""
+        return {**{"left." + k: v for k, v in self.left.names.items()}, **{"right." + k: v for k, v in self.right.names.items()}}
 
 
 @dataclass(frozen=True)
@@ -211,6 +283,32 @@ class GatedMlpSpec:
 
 
 @dataclass(frozen=True)
+class HyperConnectionSpec:
+    """How one sublayer meets a residual stream kept in `streams` copies x_1 .. x_S: it reads u = sum_s in[s] x_s and its
+    result y returns as x_t <- sum_s mix[s][t] x_s + out[t] * (scale . y) for all t at once, `scale` a vector of the
+    width (`layer_scale`).  `mixing` False: no in, mix, out tensors (ones, the identity, ones), which with one copy is the
+    plain residual sum."""
+    streams: int
+    width: int
+    mixing: bool = True
+    layer_scale: bool = True
+    kind: str = "hyper_connection"
+    names: Mapping[str, str] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class StreamSumNormSpec:
+    """The RMS norm of the sum of a residual stream's `streams` copies (one row holds them side by side):
+    x = sum_s x_s; x / sqrt(mean(x^2) + eps) * (offset + weight)."""
+    size: int
+    streams: int
+    eps: float
+    offset: float = 0.0
+    kind: str = "stream_sum_rmsnorm"
+    names: Mapping[str, str] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
 class RoutedExpertsSpec:
     """A mixture of `n_experts` small feed-forward layers W_down act(W_up h) without biases, of which a token uses `top`.
 
@@ -245,12 +343,15 @@ class BlockSpec:
     arrangement "sandwich": a norm before and after each sublayer, x in 32-bit:
         x += norm_1b(mixer(norm_1(x))); x += norm_2b(ffn(norm_2(x)))
                                         (norms: "input", "post_input", and with a feed-forward "post_mixer", "post_ffn")
+    arrangement "hyper": the stream in several copies, in 32-bit; each sublayer reads and writes it as its
+        `HyperConnectionSpec` says (`connections`: "mixer", and with a feed-forward "ffn"); norms "input", "post_mixer".
     """
     mixer: object
     ffn: object
     norms: Mapping[str, object]
     arrangement: str = "parallel"
     residual_scale: float = 1.0
+    connections: Mapping[str, object] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
@@ -296,6 +397,7 @@ class NormedEmbeddingSpec:
     eps: float
     center: bool = True
     stream_dtype: Optional[str] = None
+    offset: float = 0.0                 # RMS only: the weight is stored around zero (offset 1)
     kind: str = "normed_embedding"
     names: Mapping[str, str] = field(default_factory=dict)
 

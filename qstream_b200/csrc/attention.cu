@@ -26,8 +26,9 @@ __global__ void rope_store_kernel(T* __restrict__ q, const T* __restrict__ k, co
                                   const int32_t* __restrict__ page_table, int max_pages, int page_shift,
                                   T* __restrict__ k_cache, T* __restrict__ v_cache,
                                   int32_t* __restrict__ status, int dv, const T* __restrict__ v_first, size_t ldvf,
-                                  float lam) {
+                                  float lam, int half_layout) {
     // blockIdx.x = token; the gridDim.y blocks of a token share its (head, pair of dims) items of q, then k and v
+    // half_layout: the rotated pairs are (j, j + R/2) instead of (2j, 2j+1); the angles are the same
     grid_dep_launch();
     grid_dep_wait();
     const int t = blockIdx.x;
@@ -47,9 +48,10 @@ __global__ void rope_store_kernel(T* __restrict__ q, const T* __restrict__ k, co
             const int head = e / rp, j = e - head * rp;
             T* row = q + (size_t)t * ldq + (size_t)head * dh;
             const float c = cs[2 * j], sn = cs[2 * j + 1];
-            const float a = to_f32(row[2 * j]), b = to_f32(row[2 * j + 1]);
-            row[2 * j] = from_f32<T>(a * c - b * sn);
-            row[2 * j + 1] = from_f32<T>(a * sn + b * c);
+            const int ia = half_layout ? j : 2 * j, ib = half_layout ? j + rp : 2 * j + 1;
+            const float a = to_f32(row[ia]), b = to_f32(row[ib]);
+            row[ia] = from_f32<T>(a * c - b * sn);
+            row[ib] = from_f32<T>(a * sn + b * c);
         }
     }
     if (n_kv_heads == 0) return;
@@ -61,7 +63,18 @@ __global__ void rope_store_kernel(T* __restrict__ q, const T* __restrict__ k, co
         const size_t dst_off = (((size_t)page * n_kv_heads + kvh) * page_tokens + in_page) * dh;
         const T* krow = k + (size_t)t * ldk + (size_t)kvh * dh;
         T* kdst = k_cache + dst_off;
-        if (rotate && 2 * j < R) {
+        if (half_layout) {                  // item j: the pair (j, j + R/2) while j < R/2, then two plain elements
+            const int rp = rotate ? R >> 1 : 0;
+            if (j < rp) {
+                const float c = cs[2 * j], sn = cs[2 * j + 1];
+                const float a = to_f32(krow[j]), b = to_f32(krow[j + rp]);
+                kdst[j] = from_f32<T>(a * c - b * sn);
+                kdst[j + rp] = from_f32<T>(a * sn + b * c);
+            } else {
+                kdst[2 * j] = krow[2 * j];
+                kdst[2 * j + 1] = krow[2 * j + 1];
+            }
+        } else if (rotate && 2 * j < R) {
             const float c = cs[2 * j], sn = cs[2 * j + 1];
             const float a = to_f32(krow[2 * j]), b = to_f32(krow[2 * j + 1]);
             kdst[2 * j] = from_f32<T>(a * c - b * sn);
@@ -191,28 +204,36 @@ __global__ void rope_store_vec_kernel(__nv_bfloat16* __restrict__ q, const __nv_
 // token's own position, never on the batch or on where the pages lie.
 // Lane l owns output dims l, l+32, ...: NACC = ceil(dv / 32) accumulators (dv: the values' head size).
 // softcap > 0: s <- softcap * tanh(s / softcap) before the softmax.
-template <typename T, int NACC>
+// Which keys a query at position p sees: first .. p, where first = p - window + 1 (window > 0), or the start of
+// p's chunk (chunk > 0: chunks of that many positions counted from 0), or 0; and, with keep_first > 0, the keys
+// 0 .. keep_first - 1 below `first` as well.  sink: one number per query head whose exponential joins the softmax's
+// denominator without a key or a value.  maps > 1: a key row holds `maps` keys of dh side by side; query head j
+// reads key number j % maps of key head (j / maps) / (heads per key head), and that key head's values.
+// TO: the type of the result (that of q and the cache, or 32-bit where a later kernel still works on it).
+template <typename T, int NACC, typename TO>
 __global__ void __launch_bounds__(128)
-attention_kernel(T* __restrict__ out, const T* __restrict__ q, size_t ldo, size_t ldq,
+attention_kernel(TO* __restrict__ out, const T* __restrict__ q, size_t ldo, size_t ldq,
                  const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                  const int32_t* __restrict__ page_table, int max_pages, int page_shift,
                  const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
                  int T_tokens, int n_heads, int n_kv_heads, int dh, float scale, int window,
-                 int32_t* __restrict__ status, int dv, float softcap) {
+                 int32_t* __restrict__ status, int dv, float softcap, int chunk, int keep_first,
+                 const float* __restrict__ sink, int maps) {
     extern __shared__ float q_smem[];               // [warps][dh]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int warps = blockDim.x >> 5;
     const long long item = (long long)blockIdx.x * warps + warp;
     if (item >= (long long)T_tokens * n_heads) return;
     const int t = (int)(item / n_heads), head = (int)(item % n_heads);
-    T* o = out + (size_t)t * ldo + (size_t)head * dv;
+    TO* o = out + (size_t)t * ldo + (size_t)head * dv;
     const int slot = tok_slot[t];
     if (slot < 0) {                                 // padding: defined output, no cache access
-        for (int d = lane; d < dv; d += 32) o[d] = from_f32<T>(0.f);
+        for (int d = lane; d < dv; d += 32) o[d] = from_f32<TO>(0.f);
         return;
     }
     const int pos = tok_pos[t];
-    const int kvh = head / (n_heads / n_kv_heads);  // QStream src/engine.c:884,889
+    const int kvh = (head / maps) / (n_heads / maps / n_kv_heads);  // QStream src/engine.c:884,889
+    const int krow_width = dh * maps, k_off = (head % maps) * dh;
     const int page_tokens = 1 << page_shift;
     const int32_t* pages = page_table + (size_t)slot * max_pages;
 
@@ -225,11 +246,14 @@ attention_kernel(T* __restrict__ out, const T* __restrict__ q, size_t ldo, size_
 #pragma unroll
     for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
     float m = -INFINITY, l = 0.f;
-    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    const int first = window > 0 ? max(0, pos - window + 1) : (chunk > 0 ? pos - pos % chunk : 0);
+    const int kept = min(keep_first, first);        // keys 0 .. kept - 1 are seen besides first .. pos
 
-    for (int base = first; base <= pos; base += 32) {
+    for (int seg = kept > 0 ? 0 : 1; seg < 2; ++seg) {
+    const int seg_lo = seg == 0 ? 0 : first, seg_hi = seg == 0 ? kept : pos + 1;
+    for (int base = seg_lo; base < seg_hi; base += 32) {
         const int key = base + lane;
-        const bool live = key <= pos;
+        const bool live = key < seg_hi;
         float s = -INFINITY;
         const T* vrow = nullptr;
         if (live) {
@@ -237,7 +261,7 @@ attention_kernel(T* __restrict__ out, const T* __restrict__ q, size_t ldo, size_
             if (page < 0) { atomicExch(status, 3); }
             else {
                 const size_t off = ((size_t)page * n_kv_heads + kvh) * page_tokens + (key & (page_tokens - 1));
-                const T* krow = k_cache + off * dh;
+                const T* krow = k_cache + off * krow_width + k_off;
                 vrow = v_cache + off * dv;
                 float dot = 0.f;
                 for (int d = 0; d < dh; ++d) dot = fmaf(qs[d], to_f32(krow[d]), dot);
@@ -251,7 +275,7 @@ attention_kernel(T* __restrict__ out, const T* __restrict__ q, size_t ldo, size_
         l = l * alpha + warp_sum(p);
 #pragma unroll
         for (int i = 0; i < NACC; ++i) acc[i] *= alpha;
-        const int n_keys = min(32, pos - base + 1);
+        const int n_keys = min(32, seg_hi - base);
         for (int j = 0; j < n_keys; ++j) {
             const float pj = __shfl_sync(0xffffffffu, p, j);
             const T* vj = reinterpret_cast<const T*>(__shfl_sync(0xffffffffu, (unsigned long long)vrow, j));
@@ -264,28 +288,37 @@ attention_kernel(T* __restrict__ out, const T* __restrict__ q, size_t ldo, size_
         }
         m = m_new;
     }
+    }
+    if (sink) {
+        const float sk = sink[head];
+        const float m_new = fmaxf(m, sk);
+        const float alpha = m == -INFINITY ? 0.f : expf(m - m_new);
+        l = l * alpha + expf(sk - m_new);
+#pragma unroll
+        for (int i = 0; i < NACC; ++i) acc[i] *= alpha;
+    }
     const float inv = l > 0.f ? 1.0f / l : 0.f;
 #pragma unroll
     for (int i = 0; i < NACC; ++i) {
         const int d = lane + 32 * i;
-        if (d < dv) o[d] = from_f32<T>(acc[i] * inv);
+        if (d < dv) o[d] = from_f32<TO>(acc[i] * inv);
     }
 }
 
-template <typename T>
+template <typename T, typename TO>
 int launch_attention(void* out, const void* q, long long ldo, long long ldq, const void* k_cache,
                      const void* v_cache, const int32_t* page_table, int max_pages, int page_shift,
                      const int32_t* tok_slot, const int32_t* tok_pos, int T_tokens, int n_heads,
                      int n_kv_heads, int dh, float scale, int window, int32_t* status, int dv, float softcap,
-                     cudaStream_t stream) {
+                     int chunk, int keep_first, const float* sink, int maps, cudaStream_t stream) {
     const int warps = 4;
     const long long items = (long long)T_tokens * n_heads;
     const int blocks = (int)((items + warps - 1) / warps);
     const size_t smem = (size_t)warps * dh * sizeof(float);
-#define GO(NACC) attention_kernel<T, NACC><<<blocks, warps * 32, smem, stream>>>( \
-        (T*)out, (const T*)q, (size_t)ldo, (size_t)ldq, (const T*)k_cache, (const T*)v_cache, \
+#define GO(NACC) attention_kernel<T, NACC, TO><<<blocks, warps * 32, smem, stream>>>( \
+        (TO*)out, (const T*)q, (size_t)ldo, (size_t)ldq, (const T*)k_cache, (const T*)v_cache, \
         page_table, max_pages, page_shift, tok_slot, tok_pos, T_tokens, n_heads, n_kv_heads, dh, \
-        scale, window, status, dv, softcap)
+        scale, window, status, dv, softcap, chunk, keep_first, sink, maps)
     const int nacc = (dv + 31) / 32;
     if (nacc <= 1) GO(1);
     else if (nacc <= 2) GO(2);
@@ -307,7 +340,8 @@ QS_API int qs_rope_store(void* q, const void* k, const void* v, int dtype,
                          const int32_t* tok_slot, const int32_t* tok_pos,
                          const int32_t* page_table, int max_pages, int page_tokens,
                          void* k_cache, void* v_cache, int T_tokens, int32_t* status,
-                         int settled, int dv, const void* v_first, long long ldvf, float lam, cudaStream_t stream) {
+                         int settled, int dv, const void* v_first, long long ldvf, float lam, int half_layout,
+                         cudaStream_t stream) {
     if (T_tokens == 0) return QS_OK;
     if (dv <= 0) dv = dh;
     QS_REQUIRE(T_tokens > 0 && n_heads >= 0 && n_kv_heads >= 0 && n_heads + n_kv_heads > 0 && dh > 0, "rope_store: bad sizes");
@@ -326,7 +360,7 @@ QS_API int qs_rope_store(void* q, const void* k, const void* v, int dtype,
                          ldvf % 8 == 0 && ((uintptr_t)v_first % 16) == 0 &&
                          ((uintptr_t)q % 16) == 0 && ((uintptr_t)k % 16) == 0 && ((uintptr_t)v % 16) == 0 &&
                          ((uintptr_t)k_cache % 16) == 0 && ((uintptr_t)v_cache % 16) == 0 && ((uintptr_t)cos_sin % 16) == 0;
-    if (dtype == QS_BF16 && aligned) {
+    if (dtype == QS_BF16 && aligned && !(half_layout && R > 0)) {
         const int work8 = (n_heads * (R / 8) + n_kv_heads * ((dh + dv) / 16));
         const int threads8 = work8 >= 512 ? 128 : 64;
         int per = 1;
@@ -341,12 +375,13 @@ QS_API int qs_rope_store(void* q, const void* k, const void* v, int dtype,
     if (dtype == QS_F32)
         qs_launch_dependent(rope_store_kernel<float>, grid, dim3(threads), 0, stream, (float*)q, (const float*)k, (const float*)v,
             (size_t)ldq, (size_t)ldk, (size_t)ldv, n_heads, n_kv_heads, dh, R, cos_sin, max_pos, tok_slot, tok_pos,
-            page_table, max_pages, shift, (float*)k_cache, (float*)v_cache, status, dv, (const float*)v_first, (size_t)ldvf, lam);
+            page_table, max_pages, shift, (float*)k_cache, (float*)v_cache, status, dv, (const float*)v_first, (size_t)ldvf, lam,
+            half_layout);
     else if (dtype == QS_BF16)
         qs_launch_dependent(rope_store_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (__nv_bfloat16*)q, (const __nv_bfloat16*)k,
             (const __nv_bfloat16*)v, (size_t)ldq, (size_t)ldk, (size_t)ldv, n_heads, n_kv_heads, dh, R, cos_sin, max_pos,
             tok_slot, tok_pos, page_table, max_pages, shift, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, status, dv,
-            (const __nv_bfloat16*)v_first, (size_t)ldvf, lam);
+            (const __nv_bfloat16*)v_first, (size_t)ldvf, lam, half_layout);
     else return qs_fail(QS_ERR_INVALID_INPUT, "rope_store: unknown dtype %d", dtype);
     return qs_check_launch("rope_store");
 }
@@ -356,11 +391,18 @@ QS_API int qs_attention(void* out, const void* q, int dtype, long long ldo, long
                         const int32_t* page_table, int max_pages, int page_tokens,
                         const int32_t* tok_slot, const int32_t* tok_pos, int T_tokens,
                         int n_heads, int n_kv_heads, int dh, float scale, int window,
-                        int32_t* status, int dv, float softcap, cudaStream_t stream) {
+                        int32_t* status, int dv, float softcap, int chunk, int keep_first, const float* sink,
+                        int maps, int out_dtype, cudaStream_t stream) {
     if (T_tokens == 0) return QS_OK;
     if (dv <= 0) dv = dh;
+    if (maps <= 0) maps = 1;
+    if (out_dtype < 0) out_dtype = dtype;
+    QS_REQUIRE(out_dtype == dtype || out_dtype == QS_F32, "attention: a result of type %d from queries of type %d", out_dtype, dtype);
     QS_REQUIRE(dv <= 512, "attention: value head size %d above 512", dv);
     QS_REQUIRE(T_tokens > 0 && n_heads > 0 && n_kv_heads > 0 && dh > 0, "attention: bad sizes");
+    QS_REQUIRE(chunk >= 0 && keep_first >= 0 && !(chunk > 0 && window > 0), "attention: a window of %d and chunks of %d", window, chunk);
+    QS_REQUIRE(n_heads % maps == 0 && (n_heads / maps) % n_kv_heads == 0, "attention: %d query heads in %d maps over %d key heads",
+               n_heads, maps, n_kv_heads);
     QS_REQUIRE(n_heads % n_kv_heads == 0, "attention: %d query heads are no multiple of %d key heads", n_heads, n_kv_heads);
     QS_REQUIRE(dh <= 2048, "attention: head size %d above 2048", dh);      // a warp's query in shared memory: 4 warps x dh floats
     QS_REQUIRE(page_tokens > 0 && (page_tokens & (page_tokens - 1)) == 0, "attention: page size %d is no power of two", page_tokens);
@@ -368,11 +410,59 @@ QS_API int qs_attention(void* out, const void* q, int dtype, long long ldo, long
     int shift = 0;
     while ((1 << shift) < page_tokens) ++shift;
     if (dtype == QS_F32)
-        return launch_attention<float>(out, q, ldo, ldq, k_cache, v_cache, page_table, max_pages, shift, tok_slot,
-                                       tok_pos, T_tokens, n_heads, n_kv_heads, dh, scale, window, status, dv, softcap, stream);
+        return launch_attention<float, float>(out, q, ldo, ldq, k_cache, v_cache, page_table, max_pages, shift, tok_slot,
+                                       tok_pos, T_tokens, n_heads, n_kv_heads, dh, scale, window, status, dv, softcap,
+                                       chunk, keep_first, sink, maps, stream);
+    if (dtype == QS_BF16 && out_dtype == QS_F32)
+        return launch_attention<__nv_bfloat16, float>(out, q, ldo, ldq, k_cache, v_cache, page_table, max_pages, shift,
+                                                      tok_slot, tok_pos, T_tokens, n_heads, n_kv_heads, dh, scale, window,
+                                                      status, dv, softcap, chunk, keep_first, sink, maps, stream);
     if (dtype == QS_BF16)
-        return launch_attention<__nv_bfloat16>(out, q, ldo, ldq, k_cache, v_cache, page_table, max_pages, shift,
-                                               tok_slot, tok_pos, T_tokens, n_heads, n_kv_heads, dh, scale, window,
-                                               status, dv, softcap, stream);
+        return launch_attention<__nv_bfloat16, __nv_bfloat16>(out, q, ldo, ldq, k_cache, v_cache, page_table, max_pages, shift,
+                                                              tok_slot, tok_pos, T_tokens, n_heads, n_kv_heads, dh, scale, window,
+                                                              status, dv, softcap, chunk, keep_first, sink, maps, stream);
     return qs_fail(QS_ERR_INVALID_INPUT, "attention: unknown dtype %d", dtype);
+}
+
+// Two attention maps over the same values, joined: for every head, o = a1 - lam * a2, divided by its root mean
+// square over the head's dv values (eps inside the root), times `mult`.  a [rows, heads * 2 * dv], per head
+// [map 1 | map 2]; out [rows, heads * dv].  One warp per (row, head); 32-bit throughout, rounded once.
+namespace {
+template <typename TI, typename TO>
+__global__ void pair_diff_norm_kernel(TO* __restrict__ out, size_t ldo, const TI* __restrict__ a, size_t lda, int rows,
+                                      int heads, int dv, float lam, float mult, float eps) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * warps + (threadIdx.x >> 5);
+    if (item >= (long long)rows * heads) return;
+    const int r = (int)(item / heads), hd = (int)(item % heads);
+    const TI* a1 = a + (size_t)r * lda + (size_t)hd * 2 * dv;
+    const TI* a2 = a1 + dv;
+    float sq = 0.f;
+    for (int i = lane; i < dv; i += 32) { const float o = fmaf(-lam, to_f32(a2[i]), to_f32(a1[i])); sq = fmaf(o, o, sq); }
+    sq = warp_sum(sq);
+    const float f = mult / sqrtf(sq / (float)dv + eps);
+    TO* dst = out + (size_t)r * ldo + (size_t)hd * dv;
+    for (int i = lane; i < dv; i += 32) dst[i] = from_f32<TO>(fmaf(-lam, to_f32(a2[i]), to_f32(a1[i])) * f);
+}
+}  // namespace
+
+QS_API int qs_pair_diff_norm(void* out, int out_dtype, long long ldo, const void* a, int a_dtype, long long lda, int rows,
+                             int heads, int dv, float lam, float mult, float eps, cudaStream_t stream) {
+    if (rows == 0) return QS_OK;
+    QS_REQUIRE(rows > 0 && heads > 0 && dv > 0, "pair_diff_norm: bad sizes");
+    typedef __nv_bfloat16 bf16;
+    const int warps = 4;
+    const int blocks = (int)(((long long)rows * heads + warps - 1) / warps);
+    cudaError_t e;
+#define GO(TI, TO) e = qs_launch_dependent(pair_diff_norm_kernel<TI, TO>, dim3(blocks), dim3(warps * 32), 0, stream, (TO*)out, \
+                                           (size_t)ldo, (const TI*)a, (size_t)lda, rows, heads, dv, lam, mult, eps)
+    if (a_dtype == QS_F32 && out_dtype == QS_F32) GO(float, float);
+    else if (a_dtype == QS_F32 && out_dtype == QS_BF16) GO(float, bf16);
+    else if (a_dtype == QS_BF16 && out_dtype == QS_BF16) GO(bf16, bf16);
+    else return qs_fail(QS_ERR_INVALID_INPUT, "pair_diff_norm: unsupported types a=%d out=%d", a_dtype, out_dtype);
+#undef GO
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "pair_diff_norm: %s", cudaGetErrorString(e));
+    return qs_check_launch("pair_diff_norm");
 }

@@ -33,10 +33,22 @@ _SIGNATURES = {
                         c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p], c_int),
     "qs_rope_store": ([c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_longlong,
                        c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                       c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_longlong, c_float, c_void_p], c_int),
+                       c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_longlong, c_float, c_int, c_void_p], c_int),
     "qs_attention": ([c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
                       c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
-                      c_int, c_float, c_void_p], c_int),
+                      c_int, c_float, c_int, c_int, c_void_p, c_int, c_int, c_void_p], c_int),
+    "qs_pair_diff_norm": ([c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_float, c_float,
+                           c_float, c_void_p], c_int),
+    "qs_delta_prepare": ([c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int,
+                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p,
+                          c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                          c_void_p], c_int),
+    "qs_conv_state_update": ([c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
+                              c_void_p, c_void_p, c_int, c_void_p], c_int),
+    "qs_hyper_spread": ([c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p], c_int),
+    "qs_hyper_mix_norm": ([c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_longlong, c_float, c_void_p, c_longlong,
+                           c_float, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_float,
+                           c_void_p, c_int, c_longlong, c_int, c_void_p], c_int),
     "qs_residual_rmsnorm": ([c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int,
                              c_longlong, c_float, c_void_p, c_int, c_float, c_int, c_int, c_float, c_void_p], c_int),
     "qs_gated_group_norm": ([c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p, c_int, c_void_p, c_int,
@@ -49,7 +61,7 @@ _SIGNATURES = {
     "qs_state_scan": ([c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int,
                        c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
                        c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                       c_void_p, c_void_p, c_longlong, c_float, c_void_p], c_int),
+                       c_void_p, c_void_p, c_longlong, c_float, c_int, c_void_p], c_int),
     "qs_mlstm_gates": ([c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_float, c_void_p, c_longlong,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p], c_int),
     "qs_mlstm_output": ([c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int,
@@ -259,8 +271,9 @@ def linear_simt(x, weight, bias=None, activation=None, residuals=(), out_dtype=N
 
 def rope_store(q, k, v, n_heads, n_kv_heads, head_dim, rotary_dim, cos_sin, tok_slot, tok_pos,
                page_table, page_tokens, k_cache, v_cache, status, settled=False, v_head_dim=None,
-               v_first=None, v_mix=0.0) -> None:
+               v_first=None, v_mix=0.0, half_layout=False) -> None:
     """Rotate q (in place) and k, and write k and v into the paged cache entry.
+    `half_layout`: the rotated pairs are (i, i + rotary_dim / 2) instead of (2i, 2i + 1), with the same angles.
     k = v = None (n_kv_heads = 0): rotate q only (no page table is needed then).
     `v_head_dim`: the values' head size where it differs from the keys'.  `v_first` (same shape as v):
     the cache keeps (1 - v_mix) v + v_mix v_first instead of v.
@@ -277,23 +290,94 @@ def rope_store(q, k, v, n_heads, n_kv_heads, head_dim, rotary_dim, cos_sin, tok_
         _int32(page_table, "page_table") if page_table is not None else None,
         page_table.shape[1] if page_table is not None else 0, page_tokens, ptr(k_cache), ptr(v_cache), T,
         ptr(status), int(bool(settled)), int(v_head_dim or head_dim), ptr(v_first),
-        v_first.stride(0) if v_first is not None else 0, float(v_mix), stream()))
+        v_first.stride(0) if v_first is not None else 0, float(v_mix), int(bool(half_layout)), stream()))
 
 
 def attention(q, n_heads, n_kv_heads, head_dim, scale, window, tok_slot, tok_pos, page_table,
-              page_tokens, k_cache, v_cache, status, out=None, v_head_dim=None, softcap=0.0) -> torch.Tensor:
+              page_tokens, k_cache, v_cache, status, out=None, v_head_dim=None, softcap=0.0, chunk=0, keep_first=0,
+              sink=None, maps=1, out_dtype=None) -> torch.Tensor:
     """Causal attention of every token over its sequence's cache (generic kernel).  `v_head_dim`: the values'
-    head size where it differs from the keys'; `softcap` c > 0: scores become c tanh(s / c) before the softmax."""
+    head size where it differs from the keys'; `softcap` c > 0: scores become c tanh(s / c) before the softmax.
+    A query at position p sees the last `window` keys (window > 0), or the keys of its own chunk of `chunk`
+    positions counted from 0 (chunk > 0), else all up to p; with `keep_first` also the sequence's first keep_first
+    keys.  `sink` (float32 [n_heads]): exp(sink_h) joins each softmax's denominator without key or value.
+    `maps` m > 1: a cached key row holds m keys of head_dim side by side and `n_heads` counts m query heads per
+    head, query head j reading key j % m of its key head; all of them read the same values.  `out_dtype`
+    torch.float32: the result in 32-bit whatever the queries' type."""
     T = q.shape[0]
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != n_heads or not sink.is_contiguous()):
+        raise QStreamError(QsError.INVALID_INPUT, "attention: the sinks must be float32, one per query head")
     dv = int(v_head_dim or head_dim)
     if out is None:
-        out = torch.empty((T, n_heads * dv), dtype=q.dtype, device=q.device)
+        out = torch.empty((T, n_heads * dv), dtype=out_dtype or q.dtype, device=q.device)
     check(library().qs_attention(
         ptr(out), ptr(q), dtype_code(q), out.stride(0), q.stride(0), ptr(k_cache), ptr(v_cache),
         _int32(page_table, "page_table"), page_table.shape[1], page_tokens, _int32(tok_slot, "tok_slot"),
         _int32(tok_pos, "tok_pos"), T, n_heads, n_kv_heads, head_dim, float(scale), int(window),
-        ptr(status), dv, float(softcap or 0.0), stream()))
+        ptr(status), dv, float(softcap or 0.0), int(chunk), int(keep_first), ptr(sink), int(maps),
+        dtype_code(out), stream()))
     return out
+
+
+def pair_diff_norm(a, n_heads: int, value_dim: int, lam: float, mult: float, eps: float, out_dtype) -> torch.Tensor:
+    """a [T, n_heads * 2 * value_dim], per head the outputs of two attention maps side by side; returns
+    [T, n_heads * value_dim]: o = a1 - lam a2, divided by its root mean square over the head (eps inside the
+    root), times `mult`; 32-bit arithmetic, rounded once."""
+    rows, n, lda = _rows(a)
+    if n != n_heads * 2 * value_dim:
+        raise QStreamError(QsError.INVALID_INPUT, f"pair_diff_norm: width {n} is not {n_heads} x 2 x {value_dim}")
+    out = torch.empty((rows, n_heads * value_dim), dtype=out_dtype, device=a.device)
+    check(library().qs_pair_diff_norm(ptr(out), dtype_code(out), out.stride(0), ptr(a), dtype_code(a), lda, rows, n_heads,
+                                      value_dim, float(lam), float(mult), float(eps), stream()))
+    return out
+
+
+# ------------------------------------------------------------------------------- a residual stream in several copies
+
+def _f32_vector(t, n, what):
+    if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous()):
+        raise QStreamError(QsError.INVALID_INPUT, f"{what} must be {n} contiguous float32 values")
+    return ptr(t)
+
+
+def hyper_spread(src: torch.Tensor, streams: int) -> torch.Tensor:
+    """x [T, streams * D] float32 whose `streams` copies all equal src [T, D] (float32)."""
+    rows, D, lds = _rows(src)
+    if src.dtype != torch.float32:
+        raise QStreamError(QsError.INVALID_INPUT, "hyper_spread: the source must be float32")
+    x = torch.empty((rows, streams * D), dtype=torch.float32, device=src.device)
+    check(library().qs_hyper_spread(ptr(x), x.stride(0), rows, int(streams), D, ptr(src), lds, stream()))
+    return x
+
+
+def hyper_mix_norm(x, streams: int, width: int, y=None, y_scale: float = 1.0, y2=None, y2_scale: float = 1.0,
+                   layer_scale=None, mix=None, out_weights=None, in_weights=None, norm_weight=None, offset: float = 0.0,
+                   eps: float = 0.0, out_dtype=None, plain_sum: bool = False):
+    """The residual stream x [T, streams * width] (float32, `streams` copies side by side) written and read in one pass.
+    Write (y given, changed in place): x_t <- sum_s mix[s][t] x_s + out_weights[t] * layer_scale . (y_scale y + y2_scale y2).
+    Read (out_dtype given): u = sum_s in_weights[s] x_s of the new x, returned as u / sqrt(mean(u^2) + eps) * (offset +
+    norm_weight) in out_dtype, or as it is if `plain_sum`.  mix [streams, streams] ([from, to]), out_weights and
+    in_weights [streams] are float32; None stands for the identity, ones and ones.  Returns the read (None without one)."""
+    rows, n, ldx = _rows(x)
+    S, D = int(streams), int(width)
+    if x.dtype != torch.float32 or n != S * D:
+        raise QStreamError(QsError.INVALID_INPUT, f"hyper_mix_norm: the stream must be float32 [T, {S} x {D}], not {tuple(x.shape)}")
+    ldy = ldy2 = 0
+    if y is not None:
+        r1, n1, ldy = _rows(y)
+        if (r1, n1) != (rows, D):
+            raise QStreamError(QsError.INVALID_INPUT, "hyper_mix_norm: the branch differs from a copy of the stream in shape")
+    if y2 is not None:
+        r2, n2, ldy2 = _rows(y2)
+        if y is None or (r2, n2) != (rows, D) or y2.dtype != y.dtype:
+            raise QStreamError(QsError.INVALID_INPUT, "hyper_mix_norm: the second branch differs from the first")
+    h = torch.empty((rows, D), dtype=out_dtype, device=x.device) if out_dtype is not None else None
+    check(library().qs_hyper_mix_norm(
+        ptr(x), ldx, rows, S, D, ptr(y), ldy, float(y_scale), ptr(y2), ldy2, float(y2_scale), _code(y), ptr(layer_scale),
+        _code(layer_scale), _f32_vector(mix, S * S, "hyper_mix_norm: mix"), _f32_vector(out_weights, S, "hyper_mix_norm: out"),
+        _f32_vector(in_weights, S, "hyper_mix_norm: in"), ptr(norm_weight), _code(norm_weight), float(offset), float(eps),
+        ptr(h), _code(h), h.stride(0) if h is not None else 0, int(bool(plain_sum)), stream()))
+    return h
 
 
 # ------------------------------------------------------------------------------- a 32-bit residual stream, RMS norms
@@ -387,13 +471,16 @@ def keep_last_rows(dst: torch.Tensor, src: torch.Tensor, seq_start, seq_slot, n_
 
 def state_scan(mode: str, q, k, v, state, seq_start, seq_slot, n_seq, n_heads, key_dim, value_dim, head_decay=None,
                decay_logits=None, bonus=None, in_activation=None, chunks=None, token_decay=None, token_weight=None,
-               q_scale: float = 1.0) -> torch.Tensor:
+               q_scale: float = 1.0, key_decay=None, qk_group: int = 1) -> torch.Tensor:
     """Walk each sequence's tokens of this step through a per-head matrix state (float32 [slots, heads, value_dim,
     key_dim], updated in place); returns o [T, heads * value_dim] in float32.
     mode "decay": S <- decay_h S + k v^T, o = S^T q.  mode "wkv": o = (S + diag(bonus) k v^T)^T q, then
     S <- diag(exp(-exp(decay_logits))) S + k v^T.  mode "gated": S <- a_t S + b_t k v^T, o = S^T (q q_scale) with
     a = `token_decay`, b = `token_weight` (float32 [T, heads]); here `value_dim` counts one column more than v holds:
     a column of ones, whose state is the normaliser n <- a_t n + b_t k and whose output n.q is each head's last element.
+    mode "delta": S' = diag(g_t) S, u = beta_t (v - S'^T k), S <- S' + k u^T, o = S^T q, with g = `key_decay` (float32
+    [T, heads * key_dim]) and beta = `token_weight` (float32 [T, heads]); q and k hold heads / `qk_group` heads, head h
+    reading number h // qk_group; in order only (no chunks).  In mode "decay" `q_scale` multiplies q as well.
     `chunks` = (chunk_start, chunk_ids, seq_chunk, n_chunks), int32 device tensors: every sequence of the step cut
     into consecutive chunks (rows chunk_start[c] .. chunk_start[c + 1] of the packed batch; sequence s owns chunks
     seq_chunk[s] .. seq_chunk[s + 1]; chunk_ids = 0 .. n_chunks - 1).  The chunks then run side by side and a
@@ -408,16 +495,59 @@ def state_scan(mode: str, q, k, v, state, seq_start, seq_slot, n_seq, n_heads, k
         chunk_start, chunk_ids, seq_chunk, n_chunks = chunks
         chunk_state = torch.empty((n_chunks, n_heads * value_dim * key_dim), dtype=torch.float32, device=q.device)
         chunk_decay = torch.empty((n_chunks, n_heads * key_dim), dtype=torch.float32, device=q.device)
+    per_token = token_decay if token_decay is not None else token_weight
+    if mode == "delta":
+        decay_logits = key_decay
+        if chunks is not None or key_decay.dtype != torch.float32 or token_weight.dtype != torch.float32:
+            raise QStreamError(QsError.INVALID_INPUT, "state_scan: the delta rule walks in order over float32 decays and step sizes")
     if mode == "gated" and (token_decay.dtype != torch.float32 or token_decay.stride() != token_weight.stride()):
         raise QStreamError(QsError.INVALID_INPUT, "state_scan: the tokens' decays and weights must be float32 of one layout")
     check(library().qs_state_scan(
-        {"decay": 0, "wkv": 1, "gated": 2}[mode], ptr(o), o.stride(0), ptr(q), q.stride(0), ptr(k), k.stride(0), ptr(v), v.stride(0),
+        {"decay": 0, "wkv": 1, "gated": 2, "delta": 3}[mode], ptr(o), o.stride(0), ptr(q), q.stride(0), ptr(k), k.stride(0), ptr(v), v.stride(0),
         dtype_code(q), ptr(decay_logits), decay_logits.stride(0) if decay_logits is not None else 0, ptr(head_decay),
         ptr(bonus), _code(bonus), ptr(state), state.stride(0), _int32(seq_start, "seq_start"),
         _int32(seq_slot, "seq_slot"), int(n_seq), T, n_heads, key_dim, value_dim, ACTIVATIONS[in_activation],
         ptr(chunk_start), ptr(chunk_ids), int(n_chunks), ptr(seq_chunk), ptr(chunk_state), ptr(chunk_decay),
-        ptr(token_decay), ptr(token_weight), token_decay.stride(0) if token_decay is not None else 0, float(q_scale), stream()))
+        ptr(token_decay), ptr(token_weight), per_token.stride(0) if per_token is not None else 0, float(q_scale),
+        int(qk_group), stream()))
     return o
+
+
+def delta_prepare(q, k, v, conv_q, conv_k, conv_v, conv_state, a, b, a_log, tok_slot, tok_pos, n_qk_heads, n_heads,
+                  key_dim, value_dim, q_scale: float, unit_eps: float):
+    """What a gated delta rule needs between its projections and its scan.  q, k [T, n_qk_heads * key_dim] and v
+    [T, n_heads * value_dim] (views of one product's result) pass a causal convolution over time per channel (taps
+    [channels, n], the last column the current token's; the n - 1 inputs before a step's first token come from
+    `conv_state` [slots, n - 1, channels of q | k | v]) and silu; q and k become unit vectors per head
+    (x / sqrt(sum x^2 + unit_eps)), q times q_scale.  a float32 [T, n_heads * key_dim] gives the decays
+    exp(-exp(a_log_h) softplus(a)), b float32 [T, n_heads] the step sizes sigmoid(b).  Returns float32 q, k, v, decays,
+    step sizes.  Call `conv_state_update` afterwards."""
+    T = q.shape[0]
+    nq, nv = n_qk_heads * key_dim, n_heads * value_dim
+    taps = conv_q.shape[1]
+    if q.stride(0) != k.stride(0) or q.stride(0) != v.stride(0) or not (conv_q.dtype == conv_k.dtype == conv_v.dtype):
+        raise QStreamError(QsError.INVALID_INPUT, "delta_prepare: q, k, v must be views of one product")
+    if a.dtype != torch.float32 or b.dtype != torch.float32:
+        raise QStreamError(QsError.INVALID_INPUT, "delta_prepare: the decays' and step sizes' inputs must be float32")
+    f32 = dict(dtype=torch.float32, device=q.device)
+    qo, ko, vo = torch.empty((T, nq), **f32), torch.empty((T, nq), **f32), torch.empty((T, nv), **f32)
+    go, bo = torch.empty((T, n_heads * key_dim), **f32), torch.empty((T, n_heads), **f32)
+    check(library().qs_delta_prepare(
+        ptr(qo), ptr(ko), ptr(vo), ptr(go), ptr(bo), ptr(q), ptr(k), ptr(v), q.stride(0), dtype_code(q), ptr(conv_q),
+        ptr(conv_k), ptr(conv_v), dtype_code(conv_q), taps, ptr(conv_state), conv_state.stride(0) if conv_state is not None else 0,
+        ptr(a), a.stride(0), ptr(b), b.stride(0), ptr(a_log), dtype_code(a_log), _int32(tok_slot, "tok_slot"),
+        _int32(tok_pos, "tok_pos"), T, n_qk_heads, n_heads, key_dim, value_dim, float(q_scale), float(unit_eps), stream()))
+    return qo, ko, vo, go, bo
+
+
+def conv_state_update(conv_state, q, k, v, n_qk: int, n_v: int, taps: int, seq_start, seq_slot, n_seq: int) -> None:
+    """Leave in `conv_state` [slots, taps - 1, 2 n_qk + n_v] the last taps - 1 inputs (q | k | v, before the
+    convolution) of what each of the step's sequences held and the step brought."""
+    if taps <= 1:
+        return
+    check(library().qs_conv_state_update(ptr(conv_state), conv_state.stride(0), ptr(q), ptr(k), ptr(v), q.stride(0),
+                                         dtype_code(q), int(n_qk), int(n_v), int(taps), _int32(seq_start, "seq_start"),
+                                         _int32(seq_slot, "seq_slot"), int(n_seq), stream()))
 
 
 def mlstm_gates(raw, cap: float, m_state, seq_start, seq_slot, n_seq: int, n_heads: int):

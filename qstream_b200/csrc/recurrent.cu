@@ -8,6 +8,11 @@
 //   gates are turned into the factors a_t, b_t by `mlstm_gates_kernel`):
 //       S_t = a_t S_{t-1} + b_t k_t v_t^T,   o_t = S_t^T (q_t * q_scale);   the last column of S has v = 1 and so
 //       carries the normaliser n_t = a_t n_{t-1} + b_t k_t, whose product with q arrives as the last element of o
+//   delta rule with a decay per token and key channel and a step size per token and head ("delta"):
+//       S' = diag(g_t) S_{t-1},   u_t = beta_t (v_t - S'^T k_t),   S_t = S' + k_t u_t^T,   o_t = S_t^T q_t
+//       (q, k, v arrive ready: activated, normed, scaled; several heads may share one head of q and k).  A column of S
+//       does not meet the others, so the threads of a column pair take S'^T k, S'^T q and k.q in one round of
+//       shuffles, and o_t = S'^T q + u_t (k.q).  In order only (PHASE 0).
 //
 // The state lives in 32-bit, per slot as [heads][dv][dk] (a column of S is contiguous), starts at zero and is
 // read at the start of a step and written back at its end; everything between the projections and the output is
@@ -43,20 +48,21 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
                   float* __restrict__ state, size_t slot_stride,
                   const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot, int n_seq, int T_rows,
                   int H, int dk, int dv, int ks_log2, int cols, int in_act, int vec,
-                  const float* __restrict__ ga, const float* __restrict__ gb, size_t ldg, float q_scale) {
-    constexpr bool WKV = MODE == 1, GATED = MODE == 2;
+                  const float* __restrict__ ga, const float* __restrict__ gb, size_t ldg, float q_scale, int qk_group) {
+    constexpr bool WKV = MODE == 1, GATED = MODE == 2, DELTA = MODE == 3;
     extern __shared__ float smem[];
     const int KS = 1 << ks_log2, dkp = KS * RK;
     float* sq = smem;                                   // [TILE][dkp]
     float* sk = sq + TILE * dkp;                        // [TILE][dkp]
     float* sw = sk + TILE * dkp;                        // [TILE][dkp]   (WKV only)
-    float* sv = sw + (WKV ? TILE * dkp : 0);            // [TILE][cols]
+    float* sv = sw + (WKV || DELTA ? TILE * dkp : 0);   // [TILE][cols]
     float* carry = sv + TILE * cols;                    // [dkp]         (PHASE 3: the decay from the chunk's start on)
     float* sa = carry + dkp;                            // [TILE]        (GATED: the tokens' decays)
     const int dvv = GATED ? dv - 1 : dv;                // columns that v holds per head: the gated form adds one of ones
     grid_dep_launch();
     grid_dep_wait();
     const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * cols;
+    const int hq = DELTA ? h / qk_group : h;            // the head of q and k that this head reads
     const int n_cols = min(cols, dv - col0);
     const int tid = threadIdx.x;
     // rows of the packed batch beyond the last sequence belong to nobody: give them a defined value
@@ -115,9 +121,9 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
             for (int tt = 0; tt < TILE; ++tt) {
                 if (tt < nt && i < dk) {
                     const size_t row = (size_t)(base + tt);
-                    qraw[tt] = q[row * ldq + h * dk + i];
-                    if (PHASE != 3) kraw[tt] = k[row * ldk + h * dk + i];
-                    if (WKV) draw[tt] = dlog[row * ldd + h * dk + i];
+                    qraw[tt] = q[row * ldq + hq * dk + i];
+                    if (PHASE != 3) kraw[tt] = k[row * ldk + hq * dk + i];
+                    if (WKV || DELTA) draw[tt] = dlog[row * ldd + h * dk + i];
                     if (GATED) draw[tt] = (PHASE == 3 ? ga : gb)[row * ldg + h];
                 }
             }
@@ -130,7 +136,9 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
                         qv = apply_activation(to_f32(qraw[tt]), in_act);
                         if (PHASE != 3) kv = apply_activation(to_f32(kraw[tt]), in_act);
                         if (WKV) wv = expf(-expf(draw[tt]));
-                        if (GATED) { qv *= q_scale; if (PHASE != 3) kv *= draw[tt]; }
+                        if (DELTA) wv = draw[tt];
+                        if (!WKV && !DELTA) qv *= q_scale;      // a constant factor on q (or, the sums being bilinear, on k)
+                        if (GATED && PHASE != 3) kv *= draw[tt];
                     }
                     if (PHASE == 3) {
                         if (WKV) { qv *= run; run *= wv; }
@@ -138,7 +146,7 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
                         else { run *= decay; qv *= run; }
                     } else {
                         sk[tt * dkp + i] = kv;
-                        if (WKV) sw[tt * dkp + i] = wv;
+                        if (WKV || DELTA) sw[tt * dkp + i] = wv;
                     }
                     sq[tt * dkp + i] = qv;
                 }
@@ -152,6 +160,7 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
                         : apply_activation(to_f32(v[(size_t)(base + tt) * ldv + h * dvv + col0 + c]), in_act);
             }
             if (GATED && tid < nt) sa[tid] = ga[(size_t)(base + tid) * ldg + h];
+            if (DELTA && tid < nt) sa[tid] = gb[(size_t)(base + tid) * ldg + h];
         }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
@@ -161,6 +170,45 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
             const float4* k4 = reinterpret_cast<const float4*>(sk + tt * dkp) + ks;
             const float4* w4 = reinterpret_cast<const float4*>(sw + tt * dkp) + ks;
             float acc0 = 0.f, acc1 = 0.f;
+            if (DELTA) {
+                float a0 = 0.f, a1 = 0.f, kq = 0.f;
+#pragma unroll
+                for (int r4 = 0; r4 < RK / 4; ++r4) {
+                    const float4 qq = q4[r4 << ks_log2], kk = k4[r4 << ks_log2], ww = w4[r4 << ks_log2];
+                    const float qa[4] = {qq.x, qq.y, qq.z, qq.w}, ka[4] = {kk.x, kk.y, kk.z, kk.w}, wa[4] = {ww.x, ww.y, ww.z, ww.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int r = r4 * 4 + j;
+                        S0[r] *= wa[j];
+                        S1[r] *= wa[j];
+                        a0 = fmaf(ka[j], S0[r], a0);
+                        a1 = fmaf(ka[j], S1[r], a1);
+                        acc0 = fmaf(qa[j], S0[r], acc0);
+                        acc1 = fmaf(qa[j], S1[r], acc1);
+                        kq = fmaf(ka[j], qa[j], kq);
+                    }
+                }
+                for (int off = KS >> 1; off > 0; off >>= 1) {
+                    a0 += __shfl_xor_sync(0xffffffffu, a0, off);
+                    a1 += __shfl_xor_sync(0xffffffffu, a1, off);
+                    acc0 += __shfl_xor_sync(0xffffffffu, acc0, off);
+                    acc1 += __shfl_xor_sync(0xffffffffu, acc1, off);
+                    kq += __shfl_xor_sync(0xffffffffu, kq, off);
+                }
+                const float u0 = sa[tt] * (v0 - a0), u1 = sa[tt] * (v1 - a1);
+#pragma unroll
+                for (int r4 = 0; r4 < RK / 4; ++r4) {
+                    const float4 kk = k4[r4 << ks_log2];
+                    const float ka[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        S0[r4 * 4 + j] = fmaf(ka[j], u0, S0[r4 * 4 + j]);
+                        S1[r4 * 4 + j] = fmaf(ka[j], u1, S1[r4 * 4 + j]);
+                    }
+                }
+                acc0 = fmaf(u0, kq, acc0);
+                acc1 = fmaf(u1, kq, acc1);
+            } else {
 #pragma unroll
             for (int r4 = 0; r4 < RK / 4; ++r4) {
                 const float4 qq = q4[r4 << ks_log2];
@@ -198,6 +246,7 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
             for (int off = KS >> 1; off > 0; off >>= 1) {
                 acc0 += __shfl_xor_sync(0xffffffffu, acc0, off);
                 acc1 += __shfl_xor_sync(0xffffffffu, acc1, off);
+            }
             }
             if (ks == 0) {
                 // PHASE 3 adds to what PHASE 1 wrote: this thread is the element's only writer in this kernel, and a
@@ -315,8 +364,8 @@ int launch_scan(int mode, int phase, float* o, long long ldo, const void* q, lon
                 const void* v, long long ldv, const float* dlog, long long ldd, const float* head_decay, const void* bonus,
                 int bonus_dtype, float* state, long long slot_stride, const int32_t* seq_start, const int32_t* seq_slot,
                 int n_seq, int T_rows, int H, int dk, int dv, int in_act, const float* ga, const float* gb, long long ldg,
-                float q_scale, cudaStream_t stream) {
-    const bool wkv = mode == 1;
+                float q_scale, int qk_group, cudaStream_t stream) {
+    const bool wkv = mode == 1 || mode == 3;            // a decay per token and key channel, staged beside q and k
     int ks_log2 = 0;
     while ((RK << ks_log2) < dk) ++ks_log2;
     const int KS = 1 << ks_log2;
@@ -339,8 +388,9 @@ int launch_scan(int mode, int phase, float* o, long long ldo, const void* q, lon
     if (e == cudaSuccess) e = qs_launch_dependent(state_scan_kernel<TI, MODE, PHASE>, grid, dim3(threads), smem, stream, o, (size_t)ldo, \
         (const TI*)q, (size_t)ldq, (const TI*)k, (size_t)ldk, (const TI*)v, (size_t)ldv, dlog, (size_t)ldd, head_decay, bonus, \
         bonus_dtype, state, (size_t)slot_stride, seq_start, seq_slot, n_seq, T_rows, H, dk, dv, ks_log2, cols, in_act, vec, \
-        ga, gb, (size_t)ldg, q_scale); } while (0)
-    if (mode == 1) { if (phase == 0) GO(1, 0); else if (phase == 1) GO(1, 1); else GO(1, 3); }
+        ga, gb, (size_t)ldg, q_scale, qk_group); } while (0)
+    if (mode == 3) GO(3, 0);
+    else if (mode == 1) { if (phase == 0) GO(1, 0); else if (phase == 1) GO(1, 1); else GO(1, 3); }
     else if (mode == 2) { if (phase == 0) GO(2, 0); else if (phase == 1) GO(2, 1); else GO(2, 3); }
     else { if (phase == 0) GO(0, 0); else if (phase == 1) GO(0, 1); else GO(0, 3); }
 #undef GO
@@ -593,20 +643,23 @@ QS_API int qs_state_scan(int mode, float* o, long long ldo, const void* q, long 
                          const int32_t* seq_slot, int n_seq, int T_rows, int H, int dk, int dv, int in_act,
                          const int32_t* chunk_start, const int32_t* chunk_ids, int n_chunks, const int32_t* seq_chunk,
                          float* chunk_state, float* chunk_decay, const float* ga, const float* gb, long long ldg,
-                         float q_scale, cudaStream_t stream) {
+                         float q_scale, int qk_group, cudaStream_t stream) {
     if (n_seq == 0 || T_rows == 0) return QS_OK;
     QS_REQUIRE(n_seq > 0 && T_rows > 0 && H > 0 && dk > 0 && dv > 0, "state_scan: bad sizes");
     QS_REQUIRE(dk <= 16 * RK, "state_scan: %d key channels per head above %d", dk, 16 * RK);
     QS_REQUIRE(H <= 65535, "state_scan: %d heads exceed the grid", H);
-    QS_REQUIRE(mode == 0 ? head_decay != nullptr : mode == 1 ? (dlog && bonus) : (mode == 2 && ga && gb && dv > 1),
-               "state_scan: mode %d lacks its operands", mode);
+    QS_REQUIRE(mode == 0 ? head_decay != nullptr : mode == 1 ? (dlog && bonus) : mode == 2 ? (ga && gb && dv > 1)
+               : (mode == 3 && dlog && gb && !chunk_start), "state_scan: mode %d lacks its operands", mode);
+    if (qk_group < 1) qk_group = 1;
+    QS_REQUIRE(mode == 3 ? H % qk_group == 0 : qk_group == 1, "state_scan: %d heads in groups of %d", H, qk_group);
     QS_REQUIRE(dtype == QS_F32 || dtype == QS_BF16, "state_scan: unknown dtype %d", dtype);
     const bool wkv = mode == 1;
+    (void)wkv;
 #define SCAN(PHASE, STATE, STRIDE, STARTS, SLOTS, N) (dtype == QS_F32 \
         ? launch_scan<float>(mode, PHASE, o, ldo, q, ldq, k, ldk, v, ldv, dlog, ldd, head_decay, bonus, bonus_dtype, STATE, STRIDE, \
-                             STARTS, SLOTS, N, T_rows, H, dk, dv, in_act, ga, gb, ldg, q_scale, stream) \
+                             STARTS, SLOTS, N, T_rows, H, dk, dv, in_act, ga, gb, ldg, q_scale, qk_group, stream) \
         : launch_scan<__nv_bfloat16>(mode, PHASE, o, ldo, q, ldq, k, ldk, v, ldv, dlog, ldd, head_decay, bonus, bonus_dtype, STATE, \
-                                     STRIDE, STARTS, SLOTS, N, T_rows, H, dk, dv, in_act, ga, gb, ldg, q_scale, stream))
+                                     STRIDE, STARTS, SLOTS, N, T_rows, H, dk, dv, in_act, ga, gb, ldg, q_scale, qk_group, stream))
     if (!chunk_start) return SCAN(0, state, slot_stride, seq_start, seq_slot, n_seq);
     QS_REQUIRE(n_chunks > 0 && chunk_ids && seq_chunk && chunk_state && chunk_decay, "state_scan: chunks without their scratch");
     const long long per_chunk = (long long)H * dv * dk;

@@ -328,6 +328,7 @@ QS_API int qs_gated_group_norm(void* out, int out_dtype, long long ldo, const vo
 #define GO(TI, TG, TO) return launch_gated<TI, TG, TO>(out, ldo, o, ldi, w, w_dtype, gate, ldg, gate_act, rows, n, group, eps, stream)
     if (o_dtype == QS_F32 && gate_dtype == QS_F32 && out_dtype == QS_F32) GO(float, float, float);
     if (o_dtype == QS_F32 && gate_dtype == QS_BF16 && out_dtype == QS_BF16) GO(float, bf16, bf16);
+    if (o_dtype == QS_F32 && gate_dtype == QS_F32 && out_dtype == QS_BF16) GO(float, float, bf16);
     if (o_dtype == QS_BF16 && gate_dtype == QS_BF16 && out_dtype == QS_BF16) GO(bf16, bf16, bf16);
 #undef GO
     return qs_fail(QS_ERR_INVALID_INPUT, "gated_group_norm: unsupported types o=%d gate=%d out=%d", o_dtype, gate_dtype, out_dtype);

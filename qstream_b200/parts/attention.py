@@ -9,7 +9,10 @@ three projections are one matrix product over the concatenated weights.
 Options a spec may switch on, each with its constants as the spec's fields: values with a head size of
 their own; a factor on the scores other than head_dim^-1/2; a tanh cap on the scores; values blended
 with those that an earlier layer computed for the same token (what is cached is the blend); a sigmoid gate
-from the mixer's input on the concatenated heads (its projection rides in the same product as q, k, v).
+from the mixer's input on the concatenated heads (its projection rides in the same product as q, k, v); keys seen
+only inside the query's chunk of positions, or inside a window that also keeps the sequence's first tokens; a learned
+sink per head in the softmax's denominator; two attention maps per head over the same values, joined as a difference
+with a unit RMS per head (differential attention).
 """
 from __future__ import annotations
 
@@ -28,9 +31,14 @@ class Attention(Mixer):
 
     @classmethod
     def declare(cls, spec):
-        hq, hkv = spec.n_heads * spec.head_dim, spec.n_kv_heads * spec.head_dim
+        maps = getattr(spec, "maps", 1)
+        hq, hkv = spec.n_heads * maps * spec.head_dim, spec.n_kv_heads * maps * spec.head_dim
         ho, hv = spec.n_heads * spec.value_dim, spec.n_kv_heads * spec.value_dim
         d = {"q": TensorDecl((hq, spec.width)), "out": TensorDecl((spec.width, ho))}
+        if getattr(spec, "sink", False):
+            d["sink"] = TensorDecl((spec.n_heads,), "bias")
+        if maps == 2:
+            d.update({n: TensorDecl((spec.head_dim,), "bias") for n in ("lq1", "lk1", "lq2", "lk2")})
         if not spec.shares_cache:
             d["k"] = TensorDecl((hkv, spec.width))
             d["v"] = TensorDecl((hv, spec.width))
@@ -72,6 +80,20 @@ class Attention(Mixer):
         self.value_mix = float(tensors["value_mix"].float().item()) if spec.value_mix == "blend" else 0.0
         self.w_out = tensors["out"]
         self.b_out = tensors.get("out_bias") if spec.out_bias else None
+        self.maps = int(getattr(spec, "maps", 1))
+        self.chunk, self.keep_first = int(getattr(spec, "chunk", 0)), int(getattr(spec, "keep_first", 0))
+        if self.maps not in (1, 2) or (self.maps == 2 and (spec.gate or spec.value_mix or spec.shares_cache)):
+            raise QStreamError(QsError.UNSUPPORTED_ARCH, f"attention: {self.maps} maps per head with these options")
+        if self.chunk and spec.window:
+            raise QStreamError(QsError.INVALID_MODEL, "attention: chunks and a window exclude each other")
+        self.sink = tensors["sink"].float().contiguous() if getattr(spec, "sink", False) else None
+        # which of the kernels' options only the generic kernel offers
+        self.masked = bool(self.chunk or self.keep_first or self.sink is not None or self.maps > 1)
+        self.lam = 0.0
+        if self.maps == 2:                              # a constant of the model: read once, passed to the kernel by value
+            import math
+            dot = lambda a, b: float((tensors[a].double() * tensors[b].double()).sum().item())    # noqa: E731
+            self.lam = math.exp(dot("lq1", "lk1")) - math.exp(dot("lq2", "lk2")) + float(spec.diff)
         self.position = None
         if spec.position is not None:
             self.position = part_class("position", spec.position.kind)(spec.position, {}, runtime)
@@ -79,14 +101,15 @@ class Attention(Mixer):
     @property
     def cache_bytes_per_key(self) -> int:
         """What one key of a sequence costs a decode step to read: its key and its value, all heads."""
-        return self.spec.n_kv_heads * (self.spec.head_dim + self.spec.value_dim) * self.w_qkv.element_size()
+        return self.spec.n_kv_heads * (self.maps * self.spec.head_dim + self.spec.value_dim) * self.w_qkv.element_size()
 
     def kv_need(self):
         if self.spec.shares_cache:
             return None
         s = self.spec
-        return KvNeed(n_kv_heads=s.n_kv_heads, head_dim=s.head_dim, window=s.window,
-                      v_head_dim=0 if s.value_dim == s.head_dim else s.value_dim)
+        key_dim = self.maps * s.head_dim                # a cached key row holds every map's key
+        return KvNeed(n_kv_heads=s.n_kv_heads, head_dim=key_dim, window=s.window,
+                      v_head_dim=0 if s.value_dim == key_dim else s.value_dim, chunk=self.chunk, keep_first=self.keep_first)
 
     def forward(self, h, step, cache_id, residuals=(), out_dtype=None):
         o = self.forward_hidden(h, step, cache_id)
@@ -102,12 +125,15 @@ class Attention(Mixer):
         s = self.spec
         b = step.batch
         view = step.kv(cache_id)
-        hq, hkv, hv = s.n_heads * s.head_dim, s.n_kv_heads * s.head_dim, s.n_kv_heads * s.value_dim
+        hq, hkv, hv = s.n_heads * self.maps * s.head_dim, s.n_kv_heads * self.maps * s.head_dim, s.n_kv_heads * s.value_dim
         qkv = linear(h, self.w_qkv, self.b_qkv)
         q = qkv[:, :hq]
         if s.gate and out is not None:
             raise QStreamError(QsError.INVALID_INPUT, "attention: a gated mixer writes its own output")
         table = getattr(self.position, "fused_table", None) if self.position is not None else None
+        half = bool(getattr(self.position, "half_layout", False))
+        if self.maps > 1 and self.position is not None:
+            raise QStreamError(QsError.UNSUPPORTED_ARCH, "attention: several maps per head with a rotation")
         if s.shares_cache:
             if self.position is not None:
                 if table is None:
@@ -115,7 +141,7 @@ class Attention(Mixer):
                 else:                                   # rotate q only: no keys of its own
                     ops.rope_store(q, None, None, s.n_heads, 0, s.head_dim, self.position.rotary_dim, table,
                                    b.tok_slot, b.tok_pos, view.page_table, view.page_tokens, None, None,
-                                   step.status, settled=True)
+                                   step.status, settled=True, half_layout=half)
         else:
             k = qkv[:, hq:hq + hkv]
             v = qkv[:, hq + hkv:hq + hkv + hv]
@@ -128,12 +154,33 @@ class Attention(Mixer):
                     raise QStreamError(QsError.INVALID_MODEL, "attention: values to blend with, but no earlier layer kept any of this shape")
             if self.position is not None and table is None:
                 self.position.apply(q, k, step, s.n_heads, s.n_kv_heads, s.head_dim)
-            ops.rope_store(q, k, v, s.n_heads, s.n_kv_heads, s.head_dim,
+            ops.rope_store(q, k, v, s.n_heads * self.maps, s.n_kv_heads, self.maps * s.head_dim if self.maps > 1 else s.head_dim,
                            getattr(self.position, "rotary_dim", 0) if table is not None else 0, table,
                            b.tok_slot, b.tok_pos, view.page_table, view.page_tokens, view.k, view.v,
                            step.status, settled=True,     # a step's slots, positions and pages arrive before its first kernel
-                           v_head_dim=s.value_dim, v_first=v_first, v_mix=self.value_mix)
-        return attend(q, s, step, view, out, gate=qkv[:, qkv.shape[1] - s.n_heads * s.value_dim:] if s.gate else None)
+                           v_head_dim=s.value_dim, v_first=v_first, v_mix=self.value_mix, half_layout=half)
+        gate = qkv[:, qkv.shape[1] - s.n_heads * s.value_dim:] if s.gate else None
+        if not self.masked:
+            return attend(q, s, step, view, out, gate=gate)
+        return self._attend_masked(q, step, view, out, gate)
+
+    def _attend_masked(self, q, step, view, out, gate):
+        """Chunks, kept first tokens, sinks and pairs of maps: the generic kernel, every softmax in 32-bit; the two maps'
+        results stay in 32-bit until their difference has been normed."""
+        s, b = self.spec, step.batch
+        two = self.maps == 2
+        o = ops.attention(q, s.n_heads * self.maps, s.n_kv_heads, s.head_dim, s.scale, s.window, b.tok_slot, b.tok_pos,
+                          view.page_table, view.page_tokens, view.k, view.v, step.status, out=None if two or gate is not None else out,
+                          v_head_dim=s.value_dim, softcap=s.softcap, chunk=self.chunk, keep_first=self.keep_first,
+                          sink=self.sink, maps=self.maps, out_dtype=torch.float32 if two else None)
+        if two:
+            o = ops.pair_diff_norm(o, s.n_heads, s.value_dim, self.lam, 1.0 - float(s.diff), float(s.eps), q.dtype)
+        if gate is not None:
+            o = ops.gated_group_norm(o, 0, None, gate, "sigmoid", 0.0, o.dtype)
+        if out is not None and o.data_ptr() != out.data_ptr():
+            out.copy_(o)
+            return out
+        return o
 
 
 def attend(q, spec, step, view, out=None, gate=None):

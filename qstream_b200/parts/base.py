@@ -19,6 +19,8 @@ arrangement   forward(x, step, cache_id) -> x'; built from the block's parts
 embedding     forward(step) -> x [T, width] in the activations' type (or wider: a 32-bit stream), from
               step.batch.tokens (and, for position tables, step.batch.tok_pos); optional state_need()
               for state per sequence, found under step.state("embedding")
+connection    how a sublayer meets the residual stream where that is more than a sum: holds the tensors of the read
+              and the write; the arrangement that names it runs them
 head          forward(rows) -> float32 logits [n, vocab] of the wanted rows (already normalised by the
               model's final norm, if it has one); `tie(embedding)` if its spec says `tied`
 
@@ -38,7 +40,7 @@ from ..errors import QsError, QStreamError
 from ..weights.loader import TensorDecl
 
 _REGISTRY: dict[tuple[str, str], type] = {}
-ROLES = ("norm", "position", "mixer", "feed_forward", "arrangement", "embedding", "head")
+ROLES = ("norm", "position", "mixer", "feed_forward", "arrangement", "embedding", "head", "connection")
 
 
 def register(role: str, kind: str, cls: type) -> None:

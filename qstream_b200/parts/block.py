@@ -262,6 +262,131 @@ class SandwichBlock(Arrangement):
         return x
 
 
+class HyperConnection(Part):
+    """The tensors with which one sublayer meets a residual stream kept in several copies: the weights of the read
+    (`in`), of the write (`out`), the matrix that mixes the copies (`mix`, [from, to]) and the vector that scales the
+    sublayer's result.  All are used in 32-bit."""
+    role = "connection"
+    captures_any_step = True
+
+    @classmethod
+    def declare(cls, spec):
+        from ..weights.loader import TensorDecl
+        S = spec.streams
+        d = {}
+        if spec.layer_scale:
+            d["scale"] = TensorDecl((spec.width,), "norm_weight")
+        if spec.mixing:
+            # drawn at random, the copies are averaged (S = 2) and read and written with weights around one
+            d.update({"in": TensorDecl((S,), "norm_weight"), "out": TensorDecl((S,), "norm_weight"),
+                      "mix": TensorDecl((S, S), "fraction")})
+        return d
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.streams, self.width = int(spec.streams), int(spec.width)
+        self.scale = tensors["scale"].float().contiguous() if spec.layer_scale else None
+        self.w_in = self.w_out = self.mix = None
+        if spec.mixing:
+            self.w_in, self.w_out = tensors["in"].float().contiguous(), tensors["out"].float().contiguous()
+            self.mix = tensors["mix"].float().contiguous()
+
+
+class PendingHyperWrite:
+    """A sublayer's result (one branch, or two with a factor each) that has not yet come back into the copies of the
+    stream; the next layer's first read takes it over, anyone else applies it with a kernel of its own."""
+
+    def __init__(self, connection, branches):
+        self.connection, self.branches = connection, branches
+
+    def write_args(self):
+        c = self.connection
+        (c1, y1), (c2, y2) = (self.branches + [(1.0, None)])[:2]
+        return dict(y=y1, y_scale=c1, y2=y2, y2_scale=c2, layer_scale=c.scale, mix=c.mix, out_weights=c.w_out)
+
+    def apply(self, x):
+        from ..csrc import ops
+        c = self.connection
+        ops.hyper_mix_norm(x, c.streams, c.width, **self.write_args())
+        return x
+
+
+class HyperBlock(Arrangement):
+    """The residual stream in S copies side by side, 32-bit, [T, S * width], updated in place.  A sublayer reads
+    u = sum_s in[s] x_s, normed, and its result y (times the layer's scale vector) comes back as
+    x_t <- sum_s mix[s][t] x_s + out[t] y for all t at once.  The write of one sublayer, the read of the next and that
+    read's RMS norm are one kernel, also across layers (`step.pending`).  The first layer spreads the embedding's
+    output over the copies.  A mixer that offers `branches` (two mixers side by side) hands its results over one by
+    one with their factors, and the write adds them up.  A layer may have no feed-forward.  With one copy and no
+    mixing tensors this is the plain 32-bit residual stream with a scale vector per sublayer."""
+    norm_names = ("input",)
+    takes_pending = True
+
+    def __init__(self, spec, parts, runtime):
+        super().__init__(spec, parts, runtime)
+        import inspect
+        import torch
+        self.connections = parts["connections"]
+        if "mixer" not in self.connections or (self.ffn is not None and not {"ffn"} <= set(self.connections)):
+            raise QStreamError(QsError.INVALID_MODEL, "a hyper layer needs a connection per sublayer ('mixer', 'ffn')")
+        if self.ffn is not None and "post_mixer" not in self.norms:
+            raise QStreamError(QsError.INVALID_MODEL, "a hyper layer with a feed-forward needs the norm 'post_mixer'")
+        self.streams, self.width = self.connections["mixer"].streams, self.connections["mixer"].width
+        self.wide = torch.float32
+        self._typed = {id(p): "out_dtype" in inspect.signature(p.forward).parameters for p in (self.mixer, self.ffn) if p}
+        self.captures_any_step = self.captures_any_step and all(c.captures_any_step for c in self.connections.values())
+
+    @classmethod
+    def part_specs(cls, spec):
+        yield "mixer", spec.mixer
+        if spec.ffn is not None:
+            yield "feed_forward", spec.ffn
+        for norm_spec in spec.norms.values():
+            yield "norm", norm_spec
+        for connection in spec.connections.values():
+            yield "connection", connection
+
+    @classmethod
+    def build(cls, spec, make, runtime):
+        parts = {"mixer": make("mixer", spec.mixer), "ffn": make("feed_forward", spec.ffn) if spec.ffn is not None else None,
+                 "norms": {name: make("norm", ns) for name, ns in spec.norms.items()},
+                 "connections": {name: make("connection", cs) for name, cs in spec.connections.items()}}
+        return cls(spec, parts, runtime)
+
+    def cached_parts(self):
+        return getattr(self.mixer, "cached_parts", lambda: [self.mixer])()
+
+    def _read(self, x, connection, norm, before):
+        """The normed input of a sublayer; `before`: a write that is still pending, done in the same pass."""
+        from ..csrc import ops
+        write = before.write_args() if before is not None else {}
+        return ops.hyper_mix_norm(x, self.streams, self.width, in_weights=connection.w_in, norm_weight=norm.weight,
+                                  offset=norm.offset, eps=norm.eps, out_dtype=self.runtime.dtype, **write)
+
+    def forward(self, x, step, cache_id):
+        from ..csrc import ops
+        before, step.pending = step.pending, None
+        if before is not None and not isinstance(before, PendingHyperWrite):
+            x, before = before.apply(x), None
+        if x.shape[1] != self.streams * self.width or x.dtype != self.wide:     # the embedding's output: every copy starts as it
+            x = ops.hyper_spread(x if x.dtype == self.wide else ops.convert(x, self.wide), self.streams)
+        h = self._read(x, self.connections["mixer"], self.norms["input"], before)
+        if hasattr(self.mixer, "branches"):
+            ys = self.mixer.branches(h, step, cache_id, out_dtype=self.wide)
+        else:
+            wide = {"out_dtype": self.wide} if self._typed[id(self.mixer)] else {}
+            ys = [(1.0, self.mixer.forward(h, step, cache_id, **wide))]
+        last = PendingHyperWrite(self.connections["mixer"], ys)
+        if self.ffn is not None:
+            h = self._read(x, self.connections["ffn"], self.norms["post_mixer"], last)
+            wide = {"out_dtype": self.wide} if self._typed[id(self.ffn)] else {}
+            last = PendingHyperWrite(self.connections["ffn"], [(1.0, self.ffn.forward(h, step, **wide))])
+        step.pending = last
+        return x
+
+
+register("arrangement", "hyper", HyperBlock)
+register("connection", "hyper_connection", HyperConnection)
 register("arrangement", "parallel", ParallelBlock)
 register("arrangement", "sandwich", SandwichBlock)
 register("arrangement", "sequential", SequentialBlock)

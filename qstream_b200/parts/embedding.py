@@ -65,7 +65,8 @@ class NormedEmbedding(Embedding):
 
     @classmethod
     def declare(cls, spec):
-        return {"weight": TensorDecl((spec.vocab_size, spec.width)), "norm": TensorDecl((spec.width,), "norm_weight")}
+        return {"weight": TensorDecl((spec.vocab_size, spec.width)),
+                "norm": TensorDecl((spec.width,), "norm_delta" if getattr(spec, "offset", 0.0) else "norm_weight")}
 
     def __init__(self, spec, tensors, runtime):
         super().__init__(spec, tensors, runtime)
@@ -76,6 +77,8 @@ class NormedEmbedding(Embedding):
     def forward(self, step):
         b, s = step.batch, self.spec
         x = ops.embedding_hashed(self.weight, None, 1.0, 0, 0, 0, b.tokens, b.tok_slot, b.tok_pos, None, self.out_dtype)
+        if getattr(s, "offset", 0.0) and not s.center:      # a weight stored around zero: the RMS norm with its offset
+            return ops.rmsnorm(x, self.norm, s.eps, s.offset, out_dtype=self.out_dtype)
         return ops.branch_norm(x, self.norm, s.eps, s.center, in_place=True)
 
 

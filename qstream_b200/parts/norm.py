@@ -79,6 +79,27 @@ class StreamNorm(Norm):
         return x
 
 
+class StreamSumNorm(Norm):
+    """The RMS norm of the sum of a residual stream's copies: rows [n, streams * size] in 32-bit, the copies side by
+    side; the result [n, size] in the engine's type."""
+    captures_any_step = True
+
+    @classmethod
+    def declare(cls, spec):
+        return {"weight": TensorDecl((spec.size,), "norm_delta" if spec.offset else "norm_weight")}
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.weight = tensors["weight"]
+        self.eps, self.offset = float(spec.eps), float(spec.offset)
+
+    def forward(self, x):
+        s = self.spec
+        return ops.hyper_mix_norm(x, s.streams, s.size, norm_weight=self.weight, offset=self.offset, eps=self.eps,
+                                  out_dtype=self.runtime.dtype)
+
+
 register("norm", "layernorm", LayerNorm)
+register("norm", "stream_sum_rmsnorm", StreamSumNorm)
 register("norm", "stream_norm", StreamNorm)
 register("norm", "rmsnorm", RmsNorm)

@@ -9,7 +9,10 @@ two-matrix bottleneck whose output d gives the decay w = exp(-exp(d + w0)) per t
     o_t = (S_{t-1} + diag(u) k_t v_t^T)^T r_t,  S_t = diag(w_t) S_{t-1} + k_t v_t^T;
 each head's o is divided by its root mean square, then weight, silu gate, W_o.
 
-Both keep S in 32-bit per sequence (`StateNeed`), zero when a slot is taken, read at the start of a step and
+`GatedDelta` ("gated_delta"): the delta rule with a decay per token, head and key channel and a step size per token
+and head, behind short causal convolutions on q, k and v.  `PairMixer` ("pair"): two mixers side by side.
+
+All keep S in 32-bit per sequence (`StateNeed`), zero when a slot is taken, read at the start of a step and
 written at its end by one kernel that walks a sequence's tokens in order (csrc/recurrent.cu); single tokens and
 short prompts take that path, a long prompt is cut into chunks that run side by side and are joined by a prefix
 over the chunks' states.  The projections are matrix products in the engine's type; decays, the recurrence,
@@ -23,7 +26,7 @@ from ..cache import StateNeed
 from ..csrc import ops
 from ..errors import QsError, QStreamError
 from ..weights.loader import TensorDecl
-from .base import Mixer, register
+from .base import Mixer, part_class, register
 from .linear import linear
 
 
@@ -60,16 +63,22 @@ class DecayAttention(Mixer):
     @classmethod
     def declare(cls, spec):
         hk, hv = spec.n_heads * spec.key_dim, spec.n_heads * spec.value_dim
-        return {"q": TensorDecl((hk, spec.width)), "k": TensorDecl((hk, spec.width)), "v": TensorDecl((hv, spec.width)),
-                "g": TensorDecl((hv, spec.width)), "o": TensorDecl((spec.width, hv)), "norm": TensorDecl((hv,), "norm_weight")}
+        d = {"q": TensorDecl((hk, spec.width)), "k": TensorDecl((hk, spec.width)), "v": TensorDecl((hv, spec.width)),
+             "g": TensorDecl((hv, spec.width)), "o": TensorDecl((spec.width, hv))}
+        if getattr(spec, "norm_weight", True):
+            d["norm"] = TensorDecl((hv,), "norm_weight")
+        return d
 
     def __init__(self, spec, tensors, runtime):
         super().__init__(spec, tensors, runtime)
         if len(spec.decay) != spec.n_heads:
             raise QStreamError(QsError.INVALID_MODEL, f"{len(spec.decay)} decays for {spec.n_heads} heads")
         self.w_in = torch.cat([tensors[n] for n in ("q", "k", "v", "g")], dim=0).contiguous()    # one product for all four
-        self.w_out, self.norm = tensors["o"], tensors["norm"]
+        self.w_out, self.norm = tensors["o"], tensors.get("norm")
         self.decay = torch.tensor(spec.decay, dtype=torch.float32).to(runtime.device)
+        self.position = None
+        if getattr(spec, "position", None) is not None:
+            self.position = part_class("position", spec.position.kind)(spec.position, {}, runtime)
 
     def state_need(self):
         s = self.spec
@@ -78,11 +87,18 @@ class DecayAttention(Mixer):
     def forward(self, h, step, cache_id, residuals=(), out_dtype=None):
         s, b = self.spec, step.batch
         hk, hv = s.n_heads * s.key_dim, s.n_heads * s.value_dim
-        p = linear(h, self.w_in)
-        o = ops.state_scan("decay", p[:, :hk], p[:, hk:2 * hk], p[:, 2 * hk:2 * hk + hv], step.state(cache_id),
+        # a rotation enters the recurrence: q and k then leave their product in 32-bit and are rotated in 32-bit
+        p = linear(h, self.w_in, out_dtype=torch.float32 if self.position is not None else None)
+        q, k = p[:, :hk], p[:, hk:2 * hk]
+        if self.position is not None:
+            self.position.apply(q, k, step, s.n_heads, s.n_heads, s.key_dim)
+        # the factor on k rides on q: the sums are bilinear in the two
+        o = ops.state_scan("decay", q, k, p[:, 2 * hk:2 * hk + hv], step.state(cache_id),
                            b.seq_start, b.seq_slot, b.n_seq, s.n_heads, s.key_dim, s.value_dim,
-                           head_decay=self.decay, in_activation=s.activation, chunks=scan_chunks(b, h.device))
-        y = ops.gated_group_norm(o, hv, self.norm, p[:, 2 * hk + hv:], "sigmoid", s.eps, h.dtype)
+                           head_decay=self.decay, in_activation=s.activation, chunks=scan_chunks(b, h.device),
+                           q_scale=float(getattr(s, "key_scale", 1.0)))
+        group = s.value_dim if getattr(s, "norm_per_head", False) else hv
+        y = ops.gated_group_norm(o, group, self.norm, p[:, 2 * hk + hv:], getattr(s, "gate_activation", "sigmoid"), s.eps, h.dtype)
         return linear(y, self.w_out, None, residuals=residuals, out_dtype=out_dtype)
 
 
@@ -170,6 +186,107 @@ class Mlstm(Mixer):
         return linear(y, self.w_out, None, residuals=residuals, out_dtype=out_dtype)
 
 
+class GatedDelta(Mixer):
+    """The gated delta rule: S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q per head.  q, k, v and the
+    first matrices of the two bottlenecks are one product in the engine's type; the step sizes' projection and the
+    decays' second matrix give 32-bit results.  One kernel runs the short convolutions (with the inputs that earlier
+    steps left), silu, the unit norms, the decays and the step sizes, all in 32-bit; the scan walks each sequence in
+    order; the last kernel takes each head's unit RMS, the weight and the sigmoid gate."""
+    captures_any_step = True
+
+    @classmethod
+    def declare(cls, spec):
+        D, H, G, dk, dv, n = spec.width, spec.n_heads, spec.n_qk_heads, spec.key_dim, spec.value_dim, spec.conv_taps
+        return {"q": TensorDecl((G * dk, D)), "k": TensorDecl((G * dk, D)), "v": TensorDecl((H * dv, D)),
+                "conv_q": TensorDecl((G * dk, n)), "conv_k": TensorDecl((G * dk, n)), "conv_v": TensorDecl((H * dv, n)),
+                "b": TensorDecl((H, D)), "A_log": TensorDecl((H,), "bias"), "norm": TensorDecl((dv,), "norm_weight"),
+                "a1": TensorDecl((spec.decay_rank, D)), "a2": TensorDecl((H * dk, spec.decay_rank)),
+                "dt_bias": TensorDecl((H * dk,), "bias"), "g1": TensorDecl((spec.gate_rank, D)),
+                "g2": TensorDecl((H * dv, spec.gate_rank)), "o": TensorDecl((D, H * dv))}
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        if spec.n_heads % spec.n_qk_heads:
+            raise QStreamError(QsError.INVALID_MODEL, f"{spec.n_heads} heads are no multiple of {spec.n_qk_heads} heads of q and k")
+        self.w_in = torch.cat([tensors[n] for n in ("q", "k", "v", "a1", "g1")], dim=0).contiguous()
+        self.ranks = (tensors["a1"].shape[0], tensors["g1"].shape[0])
+        self.w_b, self.w_a2, self.w_g2, self.w_out = tensors["b"], tensors["a2"], tensors["g2"], tensors["o"]
+        self.dt_bias = tensors["dt_bias"].float().contiguous()
+        self.a_log = tensors["A_log"].float().contiguous()
+        self.conv = tuple(tensors["conv_" + n].contiguous() for n in ("q", "k", "v"))
+        self.norm = tensors["norm"].repeat(spec.n_heads).contiguous()       # one weight of value_dim, shared by the heads
+
+    def state_need(self):
+        s = self.spec
+        need = {"matrix": StateNeed((s.n_heads, s.value_dim, s.key_dim), torch.float32)}
+        if s.conv_taps > 1:
+            need["conv"] = StateNeed((s.conv_taps - 1, 2 * s.n_qk_heads * s.key_dim + s.n_heads * s.value_dim), self.runtime.dtype)
+        return need
+
+    def forward(self, h, step, cache_id, residuals=(), out_dtype=None):
+        s, b = self.spec, step.batch
+        nq, nv = s.n_qk_heads * s.key_dim, s.n_heads * s.value_dim
+        ra, rg = self.ranks
+        p = linear(h, self.w_in)
+        q, k, v = p[:, :nq], p[:, nq:2 * nq], p[:, 2 * nq:2 * nq + nv]
+        at = 2 * nq + nv
+        a = linear(p[:, at:at + ra], self.w_a2, self.dt_bias, out_dtype=torch.float32)
+        gate = linear(p[:, at + ra:at + ra + rg], self.w_g2, out_dtype=torch.float32)
+        beta = linear(h, self.w_b, out_dtype=torch.float32)
+        held = step.state(cache_id, "conv") if s.conv_taps > 1 else None
+        qo, ko, vo, decay, beta = ops.delta_prepare(q, k, v, *self.conv, held, a, beta, self.a_log, b.tok_slot, b.tok_pos,
+                                                    s.n_qk_heads, s.n_heads, s.key_dim, s.value_dim, s.key_dim ** -0.5, s.unit_eps)
+        if held is not None:                                # after the convolutions have read it
+            ops.conv_state_update(held, q, k, v, nq, nv, s.conv_taps, b.seq_start, b.seq_slot, b.n_seq)
+        o = ops.state_scan("delta", qo, ko, vo, step.state(cache_id, "matrix"), b.seq_start, b.seq_slot, b.n_seq,
+                           s.n_heads, s.key_dim, s.value_dim, key_decay=decay, token_weight=beta,
+                           qk_group=s.n_heads // s.n_qk_heads)
+        y = ops.gated_group_norm(o, s.value_dim, self.norm, gate, "sigmoid", s.eps, h.dtype)
+        return linear(y, self.w_out, None, residuals=residuals, out_dtype=out_dtype)
+
+
+class PairMixer(Mixer):
+    """Two mixers side by side on the same input, each with a cache entry of its own (`cache_id` is a pair):
+    left_scale * left(h) + right_scale * right(h).  An arrangement that adds branches with factors of its own asks for
+    them with `branches`; `forward` adds them up itself."""
+
+    @classmethod
+    def declare(cls, spec):
+        d = {}
+        for side, sub in (("left.", spec.left), ("right.", spec.right)):
+            d.update({side + name: decl for name, decl in part_class("mixer", sub.kind).declare(sub).items()})
+        return d
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        made = []
+        for side, sub in (("left.", spec.left), ("right.", spec.right)):
+            mine = {name[len(side):]: t for name, t in tensors.items() if name.startswith(side)}
+            made.append(part_class("mixer", sub.kind)(sub, mine, runtime))
+        self.left, self.right = made
+        self.captures_any_step = all(getattr(p, "captures_any_step", False) for p in made)
+
+    def cached_parts(self):
+        return [self.left, self.right]
+
+    def branches(self, h, step, cache_id, out_dtype=None):
+        left_id, right_id = cache_id
+        return [(float(self.spec.left_scale), self.left.forward(h, step, left_id, out_dtype=out_dtype)),
+                (float(self.spec.right_scale), self.right.forward(h, step, right_id, out_dtype=out_dtype))]
+
+    def forward(self, h, step, cache_id, residuals=(), out_dtype=None):
+        (c1, y1), (c2, y2) = self.branches(h, step, cache_id, out_dtype=torch.float32)
+        out = torch.zeros_like(y1)
+        for r in residuals:
+            if r is not None:
+                ops.rmsnorm(out, None, 0.0, update=r, mult=1.0, want_norm=False)
+        ops.rmsnorm(out, None, 0.0, update=y1, mult=c1, want_norm=False)
+        ops.rmsnorm(out, None, 0.0, update=y2, mult=c2, want_norm=False)
+        return out if out_dtype in (None, torch.float32) or out_dtype == out.dtype else ops.convert(out, out_dtype)
+
+
+register("mixer", "gated_delta", GatedDelta)
+register("mixer", "pair", PairMixer)
 register("mixer", "lightning", DecayAttention)
 register("mixer", "mlstm", Mlstm)
 register("mixer", "wkv", Wkv)

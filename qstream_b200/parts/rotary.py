@@ -47,6 +47,29 @@ class RotaryInterleaved(PositionEncoding):
                                b.tok_slot, b.tok_pos, None, 64, None, None, step.status, settled=True)
 
 
+class RotaryHalfTable(PositionEncoding):
+    """Element i of the first `rotary_dim` dims of each head is paired with element i + rotary_dim / 2, angle
+    position * base^(-2i / rotary_dim): the angles of the interleaved form, so the two share their tables; the kernel
+    is told which elements make a pair.  Attention fuses the rotation with its cache write."""
+    captures_any_step = True
+    half_layout = True
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.rotary_dim = int(spec.rotary_dim)
+        self.fused_table = _table(self.rotary_dim, spec.base, spec.max_positions, runtime.device) if self.rotary_dim > 0 else None
+
+    def apply(self, q, k, step, n_heads, n_kv_heads, head_dim):
+        """Rotate q and k in place (no cache write), in their own type."""
+        if self.fused_table is None:
+            return
+        b = step.batch
+        for x, heads in ((q, n_heads), (k, n_kv_heads)):
+            if x is not None and heads > 0:
+                ops.rope_store(x, None, None, heads, 0, head_dim, self.rotary_dim, self.fused_table,
+                               b.tok_slot, b.tok_pos, None, 64, None, None, step.status, settled=True, half_layout=True)
+
+
 def scaled_frequencies(rotary_dim: int, base: float, scaling=None):
     """The rotary_dim / 2 frequencies base^(-2i / rotary_dim) in float64, rescaled in the YaRN manner if `scaling`
     (factor, original, fast, slow) is given, and the factor on cos and sin (1 without scaling)."""
@@ -81,3 +104,4 @@ class RotaryHalf(PositionEncoding):
 
 register("position", "rotary_interleaved", RotaryInterleaved)
 register("position", "rotary_half", RotaryHalf)
+register("position", "rotary_half_table", RotaryHalfTable)
