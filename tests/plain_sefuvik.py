@@ -7,9 +7,23 @@ of the residual streams after every layer).
 """
 from __future__ import annotations
 
+import json
 import math
+from pathlib import Path
 
 import numpy as np
+
+from plain_gptj import read_safetensors
+
+
+def load_model(folder):
+    """(config dict, {tensor name: float64 array}) of a model folder (the reader is `plain_gptj`'s, also test code)."""
+    folder = Path(folder)
+    cfg = json.loads((folder / "config.json").read_text())
+    w = {}
+    for f in sorted(folder.glob("*.safetensors")):
+        w.update(read_safetensors(f))
+    return cfg, w
 
 
 # ----------------------------------------------------------------------------- small pieces
@@ -231,3 +245,15 @@ def forward(cfg, w, tokens, want_layers=False):
     z = norm_around_zero(sum(xs), w["final.norm"], eps)
     logits = z @ w["embed"].T
     return (logits, np.stack(after)) if want_layers else logits
+
+
+def logits_whole(cfg, w, tokens):
+    """Logits [T, vocab] at every position of one sequence."""
+    return forward(cfg, w, list(tokens))
+
+
+def generate_greedy(cfg, w, prompt, max_new_tokens):
+    tokens = list(prompt)
+    for _ in range(max_new_tokens):
+        tokens.append(int(np.argmax(logits_whole(cfg, w, tokens)[-1])))
+    return tokens[len(prompt):]
