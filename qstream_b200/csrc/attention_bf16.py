@@ -16,29 +16,33 @@ def _bind():
     global _decode, _scratch_size
     if _decode is None:
         _scratch_size = ops.bind("qs_attention_decode_scratch", [c_int, c_int, c_int, c_int], c_longlong)
-        _decode = ops.bind("qs_attention_decode_ex", [
+        _decode = ops.bind("qs_attention_decode_masked", [
             c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
             c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_float,
-            c_void_p, c_longlong, c_void_p])
+            c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_int, c_void_p])
 
 
 def decode(q, n_heads, n_kv_heads, head_dim, scale, window, tok_slot, tok_pos, page_table, page_tokens,
-           k_cache, v_cache, max_context, status, out=None, v_head_dim=None, softcap=0.0, gate=None) -> torch.Tensor:
+           k_cache, v_cache, max_context, status, out=None, v_head_dim=None, softcap=0.0, gate=None, chunk=0,
+           keep_first=0, sink=None, maps=1, out_dtype=None) -> torch.Tensor:
     """One query token per row against the paged cache, split over the keys and merged.  `v_head_dim`: the values'
     head size where it differs; `softcap` c > 0 caps the scores as c tanh(s / c); `gate` [T, heads * v_head_dim]:
-    the result is multiplied by sigmoid(gate) in the merge."""
+    the result is multiplied by sigmoid(gate) in the merge.  `chunk`, `keep_first`, `sink`, `maps`, `out_dtype`
+    (torch.float32 for a 32-bit result): as for `ops.attention`."""
     _bind()
     T = q.shape[0]
     dv = int(v_head_dim or head_dim)
+    wide = out_dtype == torch.float32
     if out is None:
-        out = torch.empty((T, n_heads * dv), dtype=torch.bfloat16, device=q.device)
+        out = torch.empty((T, n_heads * dv), dtype=torch.float32 if wide else torch.bfloat16, device=q.device)
     n = _scratch_size(T, n_heads, dv, max_context)
     scratch = torch.empty((n,), dtype=torch.float32, device=q.device)
     ops.check(_decode(ops.ptr(out), out.stride(0), ops.ptr(q), q.stride(0), ops.ptr(k_cache), ops.ptr(v_cache),
                       ops.ptr(page_table), page_table.shape[1], page_tokens, ops.ptr(tok_slot), ops.ptr(tok_pos),
                       T, n_heads, n_kv_heads, head_dim, float(scale), int(window), int(max_context),
                       ops.ptr(scratch), ops.ptr(status), dv, float(softcap or 0.0), ops.ptr(gate),
-                      gate.stride(0) if gate is not None else 0, ops.stream()))
+                      gate.stride(0) if gate is not None else 0, int(chunk), int(keep_first), ops.ptr(sink), int(maps),
+                      int(out.dtype == torch.float32), ops.stream()))
     ops.count_launches(1)                                   # split kernel + merge kernel
     return out
 
@@ -62,50 +66,58 @@ def prefill_tiles(batch, device) -> torch.Tensor:
 
 
 def prefill(q, n_heads, n_kv_heads, head_dim, scale, window, tiles, page_table, page_tokens, k_cache, v_cache,
-            status, padded=False, out=None, v_head_dim=None, softcap=0.0, gate=None) -> torch.Tensor:
+            status, padded=False, out=None, v_head_dim=None, softcap=0.0, gate=None, chunk=0, keep_first=0, sink=None,
+            maps=1, out_dtype=None) -> torch.Tensor:
     """Many query rows per sequence against the paged cache on the tensor cores (tcgen05).  `v_head_dim`,
-    `softcap`, `gate`: as for `decode`."""
+    `softcap`, `gate` and the rest: as for `decode`."""
     global _prefill
     if _prefill is None:
-        _prefill = ops.bind("qs_attention_prefill_ex", [
+        _prefill = ops.bind("qs_attention_prefill_masked", [
             c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
             c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_float, c_void_p, c_longlong,
-            c_void_p])
+            c_int, c_int, c_void_p, c_int, c_int, c_void_p])
     T = q.shape[0]
     dv = int(v_head_dim or head_dim)
     # rows that belong to no sequence (padding) are covered by no tile: give them a defined value
     if out is None:
-        out = torch.empty((T, n_heads * dv), dtype=torch.bfloat16, device=q.device)
+        out = torch.empty((T, n_heads * dv), dtype=torch.float32 if out_dtype == torch.float32 else torch.bfloat16, device=q.device)
     if padded:
         out.zero_()
     ops.check(_prefill(ops.ptr(out), out.stride(0), ops.ptr(q), q.stride(0), T, ops.ptr(k_cache), ops.ptr(v_cache),
                        k_cache.shape[0], ops.ptr(page_table), page_table.shape[1], page_tokens, ops.ptr(tiles),
                        tiles.shape[0], n_heads, n_kv_heads, head_dim, float(scale), int(window), ops.ptr(status),
                        dv, float(softcap or 0.0), ops.ptr(gate), gate.stride(0) if gate is not None else 0,
-                       ops.stream()))
+                       int(chunk), int(keep_first), ops.ptr(sink), int(maps), int(out.dtype == torch.float32), ops.stream()))
     return out
 
 
-def attend(q, spec, step, view, out=None, gate=None):
+def attend(q, spec, step, view, out=None, gate=None, sink=None, out_dtype=None):
     """The specialised kernel's output, or None if the generic kernel is to run.  A `gate` is applied by the
-    kernel's last stage."""
+    kernel's last stage.  The spec's chunks, kept first keys and maps per head go to the kernels as they are; `sink`
+    is the part's float32 vector; with several maps `spec.n_heads` counts heads, the kernels get heads x maps."""
     b = step.batch
     dv = spec.value_dim
-    extra = dict(v_head_dim=dv, softcap=spec.softcap, gate=gate)
-    if gate is not None and (gate.stride(0) % 8 or gate.data_ptr() % 16 or gate.dtype != torch.bfloat16):
+    maps = int(getattr(spec, "maps", 1) or 1)
+    window = spec.window
+    extra = dict(v_head_dim=dv, softcap=spec.softcap, gate=gate, chunk=int(getattr(spec, "chunk", 0) or 0),
+                 keep_first=int(getattr(spec, "keep_first", 0) or 0) if window else 0, sink=sink, maps=maps, out_dtype=out_dtype)
+    if gate is not None and (gate.stride(0) % 8 or gate.data_ptr() % 16 or gate.dtype != torch.bfloat16 or out_dtype == torch.float32):
         return None
+    if out is not None and out.dtype != (torch.float32 if out_dtype == torch.float32 else torch.bfloat16):
+        return None
+    heads = spec.n_heads * maps
     if (b.decode and view.page_tokens == 64 and spec.head_dim % 8 == 0 and spec.head_dim <= 512 and dv % 8 == 0 and dv <= 512
             and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
         # the grid covers the longest sequence of the step (a captured step: the bound it was captured for),
         # not the longest the cache allows: splits beyond it would be CTAs that start only to leave
         reach = min(b.max_total or step.cache.max_context, step.cache.max_context)
-        return decode(q, spec.n_heads, spec.n_kv_heads, spec.head_dim, spec.scale, spec.window, b.tok_slot,
+        return decode(q, heads, spec.n_kv_heads, spec.head_dim, spec.scale, spec.window, b.tok_slot,
                       b.tok_pos, view.page_table, view.page_tokens, view.k, view.v, reach,
                       step.status, out=out, **extra)
     if (not b.decode and b.slots and view.page_tokens == 64 and spec.head_dim % 16 == 0 and spec.head_dim <= 256
             and dv % 16 == 0 and dv <= 256 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
         tiles = prefill_tiles(b, q.device)
-        return prefill(q, spec.n_heads, spec.n_kv_heads, spec.head_dim, spec.scale, spec.window, tiles,
+        return prefill(q, heads, spec.n_kv_heads, spec.head_dim, spec.scale, spec.window, tiles,
                        view.page_table, view.page_tokens, view.k, view.v, step.status,
                        padded=b.n_tokens != sum(b.new_tokens), out=out, **extra)
     return None

@@ -38,9 +38,15 @@ decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict
                     const int32_t* __restrict__ page_table, int max_pages,
                     const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
                     int n_heads, int n_kv_heads, int dh, int gs_log2, float scale, int window, int max_splits,
-                    int32_t* __restrict__ status, int dv_arg, float softcap) {
-    // EXT: dv_arg is the values' head size (the keys' is dh); softcap c > 0: scores become c tanh(s / c)
+                    int32_t* __restrict__ status, int dv_arg, float softcap, int chunk_len, int keep_first, int maps_arg) {
+    // EXT: dv_arg is the values' head size (the keys' is dh); softcap c > 0: scores become c tanh(s / c);
+    // chunk_len c > 0: the query sees the keys of its own chunk of c positions (counted from 0) instead of a window;
+    // keep_first n > 0: the sequence's first n keys stay visible beside the window (every split up to the query's then
+    // writes its partial result, an empty one where it sees no key); maps_arg m > 1: a cached key row holds m keys of
+    // dh side by side, query head j reads key j % m of key head (j / m) / (heads per key head).
     const int dv = EXT ? dv_arg : dh;
+    const int maps = EXT && maps_arg > 1 ? maps_arg : 1;
+    const int keep = EXT ? keep_first : 0;
     __shared__ float s_scores[WARPS][PAGE];
     __shared__ float s_m[WARPS], s_l[WARPS];
     extern __shared__ float s_acc[];                 // [WARPS][dv]
@@ -53,14 +59,15 @@ decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict
         if (threadIdx.x == 0 && split == 0) atomicExch(status, 1);
         return;
     }
-    const int first = window > 0 ? max(0, pos - window + 1) : 0;
-    if (split * SPLIT > pos || (split + 1) * SPLIT <= first) return;       // no visible key in this split
+    const int first = (EXT && chunk_len > 0) ? pos - pos % chunk_len : window > 0 ? max(0, pos - window + 1) : 0;
+    if (split * SPLIT > pos || (keep == 0 && (split + 1) * SPLIT <= first)) return;       // no visible key in this split
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int GS = 1 << gs_log2, KPL = 32 >> gs_log2;
     const int chunk = lane & (GS - 1), sub = lane >> gs_log2;
     const int n_chunks = dh >> 3, v_chunks = EXT ? dv >> 3 : n_chunks;
-    const int kvh = head / (n_heads / n_kv_heads);
+    const int kvh = EXT ? (head / maps) / ((n_heads / maps) / n_kv_heads) : head / (n_heads / n_kv_heads);
+    const int dk_row = EXT ? maps * dh : dh;          // elements of a cached key row
 
     // this lane's part of the query, in 32-bit
     float qf[NCH][8];
@@ -83,13 +90,13 @@ decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict
     float m = -INFINITY, l = 0.f;
 
     const int key0 = split * SPLIT + warp * PAGE;     // this warp's page of keys
-    if (key0 <= pos && key0 + PAGE > first) {
+    if (key0 <= pos && (key0 + PAGE > first || key0 < keep)) {
         const int page = page_table[(size_t)slot * max_pages + (key0 >> 6)];
         if (page < 0) {
             if (lane == 0) atomicExch(status, 3);
         } else {
             const size_t base = ((size_t)page * n_kv_heads + kvh) * PAGE;
-            const __nv_bfloat16* kp = k_cache + base * dh;
+            const __nv_bfloat16* kp = k_cache + base * dk_row + (EXT ? (head % maps) * dh : 0);
             const __nv_bfloat16* vp = v_cache + base * dv;
             const int n_keys = min(PAGE, pos - key0 + 1);
             // scores of the page's keys, UNROLL warp loads in flight at a time
@@ -102,7 +109,7 @@ decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict
                     for (int i = 0; i < NCH; ++i) {
                         const int c = chunk + i * GS;
                         raw[u][i] = (kk < n_keys && c < n_chunks)
-                            ? __ldg(reinterpret_cast<const uint4*>(kp + (size_t)kk * dh + c * 8)) : make_uint4(0, 0, 0, 0);
+                            ? __ldg(reinterpret_cast<const uint4*>(kp + (size_t)kk * dk_row + c * 8)) : make_uint4(0, 0, 0, 0);
                     }
                 }
 #pragma unroll
@@ -119,7 +126,8 @@ decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict
                     for (int o = GS >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
                     float sc = dot * scale;
                     if (EXT && softcap > 0.f) sc = softcap * tanhf(sc / softcap);
-                    if (chunk == 0 && kk < PAGE) s_scores[warp][kk] = (kk < n_keys && key0 + kk >= first) ? sc : -INFINITY;
+                    if (chunk == 0 && kk < PAGE)
+                        s_scores[warp][kk] = (kk < n_keys && (key0 + kk >= first || key0 + kk < keep)) ? sc : -INFINITY;
                 }
             }
             __syncwarp();
@@ -403,21 +411,23 @@ decode_split_group_kernel(float* __restrict__ partial, const __nv_bfloat16* __re
 __global__ void decode_merge_kernel(__nv_bfloat16* __restrict__ out, size_t ldo, const float* __restrict__ partial,
                                     const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
                                     int n_heads, int dh, int window, int max_splits,
-                                    const __nv_bfloat16* __restrict__ gate, size_t ldg) {
+                                    const __nv_bfloat16* __restrict__ gate, size_t ldg, int chunk_len, int keep_first,
+                                    const float* __restrict__ sink, int out_f32) {
+    // chunk_len, keep_first: as in the split kernel.  sink (may be null): exp(sink[head]) joins the softmax's sum.
+    // out_f32: `out` holds 32-bit floats (ldo counts floats).
     grid_dep_launch();
     const int head = blockIdx.x, t = blockIdx.y;
     __nv_bfloat16* o = out + (size_t)t * ldo + (size_t)head * dh;
-    if (tok_slot[t] < 0) {
-        for (int d = threadIdx.x; d < dh; d += blockDim.x) o[d] = __float2bfloat16_rn(0.f);
+    float* o32 = reinterpret_cast<float*>(out) + (size_t)t * ldo + (size_t)head * dh;
+    const int pos = tok_slot[t] < 0 ? -1 : tok_pos[t];
+    if (pos < 0 || pos >= max_splits * SPLIT) {       // padding, or the split kernel has reported it; a defined row, no access
+        for (int d = threadIdx.x; d < dh; d += blockDim.x) {
+            if (out_f32) o32[d] = 0.f; else o[d] = __float2bfloat16_rn(0.f);
+        }
         return;
     }
-    const int pos = tok_pos[t];
-    if (pos < 0 || pos >= max_splits * SPLIT) {       // the split kernel has reported it; a defined row, no access
-        for (int d = threadIdx.x; d < dh; d += blockDim.x) o[d] = __float2bfloat16_rn(0.f);
-        return;
-    }
-    const int first = window > 0 ? max(0, pos - window + 1) : 0;
-    const int s_lo = first / SPLIT, s_hi = pos / SPLIT, n = s_hi - s_lo + 1;
+    const int first = chunk_len > 0 ? pos - pos % chunk_len : window > 0 ? max(0, pos - window + 1) : 0;
+    const int s_lo = keep_first > 0 ? 0 : first / SPLIT, s_hi = pos / SPLIT, n = s_hi - s_lo + 1;
     const float* base = partial + ((size_t)t * n_heads + head) * max_splits * (dh + 2);
     // The splits' maxima, sums and weights exp(m_s - M) are fetched and computed once per block, a split per
     // thread; every sum below then runs over shared memory or over loads that are all in flight together, in
@@ -432,11 +442,11 @@ __global__ void decode_merge_kernel(__nv_bfloat16* __restrict__ out, size_t ldo,
         s_l[i] = base[(size_t)(s_lo + i) * (dh + 2) + dh + 1];
     }
     __syncthreads();
-    float M = -INFINITY;
+    float M = sink ? sink[head] : -INFINITY;
     for (int i = 0; i < n; ++i) M = fmaxf(M, s_m[i]);
     for (int i = threadIdx.x; i < n; i += blockDim.x) s_w[i] = s_m[i] != -INFINITY ? expf(s_m[i] - M) : 0.f;
     __syncthreads();
-    float L = 0.f;
+    float L = sink ? expf(sink[head] - M) : 0.f;
     for (int i = 0; i < n; ++i)
         if (s_w[i] != 0.f) L += s_l[i] * s_w[i];
     const float inv = L > 0.f ? 1.0f / L : 0.f;
@@ -454,7 +464,7 @@ __global__ void decode_merge_kernel(__nv_bfloat16* __restrict__ out, size_t ldo,
         }
         float r = acc * inv;
         if (gate) r *= sigmoid_f32(__bfloat162float(gate[(size_t)t * ldg + (size_t)head * dh + d]));
-        o[d] = __float2bfloat16_rn(r);
+        if (out_f32) o32[d] = r; else o[d] = __float2bfloat16_rn(r);
     }
 }
 
@@ -475,13 +485,25 @@ QS_API long long qs_attention_decode_scratch(int T_tokens, int n_heads, int dh, 
 // The general form: values with a head size `dv` of their own (out [T, n_heads * dv]; the scratch is sized by dv),
 // scores capped as softcap tanh(s / softcap) when softcap > 0, and an optional sigmoid gate [T, n_heads * dv]
 // (bfloat16, row stride ldg) on the output.
-QS_API int qs_attention_decode_ex(void* out, long long ldo, const void* q, long long ldq, const void* k_cache,
-                                  const void* v_cache, const int32_t* page_table, int max_pages, int page_tokens,
-                                  const int32_t* tok_slot, const int32_t* tok_pos, int T_tokens, int n_heads,
-                                  int n_kv_heads, int dh, float scale, int window, int max_context,
-                                  float* scratch, int32_t* status, int dv, float softcap, const void* gate,
-                                  long long ldg, cudaStream_t stream) {
+//
+// The masked form adds: `chunk` c > 0 (without a window): the query sees the keys of its own chunk of c positions counted
+// from 0; `keep_first` n (with a window): the sequence's first n keys stay visible; `sink` (float32 [n_heads], may be
+// null): exp(sink_h) joins each softmax's sum without key or value; `maps` m > 1: K is [n_pages][n_kv_heads][64][m * dh]
+// and n_heads counts m query heads per head, query head j reading key j % m; `out_f32`: out is float32 (ldo in floats).
+QS_API int qs_attention_decode_masked(void* out, long long ldo, const void* q, long long ldq, const void* k_cache,
+                                      const void* v_cache, const int32_t* page_table, int max_pages, int page_tokens,
+                                      const int32_t* tok_slot, const int32_t* tok_pos, int T_tokens, int n_heads,
+                                      int n_kv_heads, int dh, float scale, int window, int max_context,
+                                      float* scratch, int32_t* status, int dv, float softcap, const void* gate,
+                                      long long ldg, int chunk, int keep_first, const float* sink, int maps, int out_f32,
+                                      cudaStream_t stream) {
     if (T_tokens == 0) return QS_OK;
+    if (maps < 1) maps = 1;
+    if (window <= 0) keep_first = 0;
+    QS_REQUIRE(chunk >= 0 && keep_first >= 0 && !(chunk > 0 && window > 0), "attention_decode: a window of %d and chunks of %d", window, chunk);
+    QS_REQUIRE(n_heads % maps == 0 && (n_heads / maps) % n_kv_heads == 0, "attention_decode: %d query heads in %d maps over %d key heads",
+               n_heads, maps, n_kv_heads);
+    const bool masked = chunk > 0 || keep_first > 0 || maps > 1;
     QS_REQUIRE(T_tokens > 0 && n_heads > 0 && n_kv_heads > 0 && dh > 0 && max_context > 0, "attention_decode: bad sizes");
     QS_REQUIRE(dv > 0 && dv % 8 == 0 && dv <= 512, "attention_decode: value head size %d must be a multiple of 8, at most 512", dv);
     QS_REQUIRE(page_tokens == PAGE, "attention_decode: pages of %d tokens, the kernel is built for %d", page_tokens, PAGE);
@@ -522,18 +544,18 @@ QS_API int qs_attention_decode_ex(void* out, long long ldo, const void* q, long 
         sm_counts[dev] = sm_count;
     }
     const bool few_ctas = (long long)max_splits * n_heads * T_tokens <= 2LL * sm_count;
-    const bool ext = dv != dh || softcap > 0.f;
+    const bool ext = dv != dh || softcap > 0.f || masked;
 #define GO(NCH, UNROLL) do { if (ext) GO1(NCH, UNROLL, true); else GO1(NCH, UNROLL, false); } while (0)
 #define GO1(NCH, UNROLL, EXT) decode_split_kernel<NCH, UNROLL, EXT><<<grid, WARPS * 32, smem, stream>>>( \
         scratch, (const __nv_bfloat16*)q, (size_t)ldq, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
         page_table, max_pages, tok_slot, tok_pos, n_heads, n_kv_heads, dh, gs_log2, scale, window, max_splits, status, \
-        dv, softcap)
+        dv, softcap, chunk, keep_first, maps)
     // Query heads that share a key head go through the pages together, two to a CTA (chunk slots of one or two per
     // lane only).  Four to a CTA were measured slower (32 x 2,048 keys, 16 query and 4 key heads of 128: 108 us
     // against 81 us with two and 96 us with one): four heads' accumulators leave room for three CTAs per SM and
     // two loads in flight per lane.
     const int per_group = n_heads / n_kv_heads;
-    const int hg = (nch <= 2 && per_group % 2 == 0) ? 2 : 1;
+    const int hg = (nch <= 2 && per_group % 2 == 0 && !masked) ? 2 : 1;      // the masked forms: a query head per CTA
 #define GROUP(NCH, UNROLL, HG) decode_split_group_kernel<NCH, UNROLL, HG><<<dim3(max_splits, n_heads / HG, T_tokens), WARPS * 32, \
         smem * HG, stream>>>(scratch, (const __nv_bfloat16*)q, (size_t)ldq, (const __nv_bfloat16*)k_cache, \
         (const __nv_bfloat16*)v_cache, page_table, max_pages, tok_slot, tok_pos, n_heads, n_kv_heads, dh, gs_log2, scale, window, \
@@ -552,8 +574,19 @@ QS_API int qs_attention_decode_ex(void* out, long long ldo, const void* q, long 
     if (rc != QS_OK) return rc;
     decode_merge_kernel<<<dim3(n_heads, T_tokens), dv >= 128 ? 128 : 64, (size_t)3 * max_splits * sizeof(float), stream>>>(
         (__nv_bfloat16*)out, (size_t)ldo, scratch, tok_slot, tok_pos, n_heads, dv, window, max_splits,
-        (const __nv_bfloat16*)gate, (size_t)ldg);
+        (const __nv_bfloat16*)gate, (size_t)ldg, chunk, keep_first, sink, out_f32);
     return qs_check_launch("attention_decode merge");
+}
+
+QS_API int qs_attention_decode_ex(void* out, long long ldo, const void* q, long long ldq, const void* k_cache,
+                                  const void* v_cache, const int32_t* page_table, int max_pages, int page_tokens,
+                                  const int32_t* tok_slot, const int32_t* tok_pos, int T_tokens, int n_heads,
+                                  int n_kv_heads, int dh, float scale, int window, int max_context,
+                                  float* scratch, int32_t* status, int dv, float softcap, const void* gate,
+                                  long long ldg, cudaStream_t stream) {
+    return qs_attention_decode_masked(out, ldo, q, ldq, k_cache, v_cache, page_table, max_pages, page_tokens, tok_slot, tok_pos,
+                                      T_tokens, n_heads, n_kv_heads, dh, scale, window, max_context, scratch, status, dv, softcap,
+                                      gate, ldg, 0, 0, nullptr, 1, 0, stream);
 }
 
 QS_API int qs_attention_decode(void* out, long long ldo, const void* q, long long ldq, const void* k_cache,

@@ -39,6 +39,7 @@ constexpr int THREADS = 320;      // producer warp, MMA warp, eight softmax warp
 constexpr float RESCALE_THRESHOLD = 8.0f;        // log2 units
 
 struct TileInfo { int row_start, n_rows, qpos0, slot; };
+struct MaskOpts { int chunk, keep_first, maps, out_f32; const float* sink; };
 
 // 2^x on the special-function unit (relative error about 2^-22; -inf gives 0).
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -69,7 +70,12 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                          const TileInfo* __restrict__ tiles, const int32_t* __restrict__ page_table, int max_pages,
                          int n_heads, int n_kv_heads, int dh, float scale_log2, int window,
                          int32_t* __restrict__ status, int dv, float cap_log2, float cap_k2,
-                         const __nv_bfloat16* __restrict__ gate, size_t ldg) {
+                         const __nv_bfloat16* __restrict__ gate, size_t ldg, const MaskOpts mask) {
+    // mask.chunk c > 0: a query sees the keys of its own chunk of c positions (counted from 0) instead of a window.
+    // mask.keep_first n > 0 (with a window): the sequence's first n keys stay visible; their blocks are walked first.
+    // mask.sink (may be null): exp(sink[head]) joins the row's sum, without a key or a value.  mask.maps m > 1: a key
+    // row holds m keys of dh side by side and query head j reads key j % m of key head (j / m) / (heads per key head).
+    // mask.out_f32: `out` holds 32-bit floats (ldo counts floats).
     // dh: head size of queries and keys, dv: of values and of the output (NKC covers the larger).  cap_log2 > 0:
     // scores are capped, s <- c tanh(s scale / c), computed as cap_log2 (1 - 2 / (2^(s cap_k2) + 1)) in log2 units
     // with cap_log2 = c log2(e) and cap_k2 = 2 log2(e) scale / c.  gate (may be null): the output row is multiplied
@@ -105,11 +111,16 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const TileInfo tile = tiles[blockIdx.y];
     if (tile.n_rows <= 0) return;             // an unused entry of a tile list of fixed length (captured steps): the whole CTA leaves
     const int head = blockIdx.x;
-    const int kvh = head / (n_heads / n_kv_heads);
+    const int maps = mask.maps > 1 ? mask.maps : 1;
+    const int kvh = (head / maps) / ((n_heads / maps) / n_kv_heads);
+    const int key_col = (head % maps) * dh;           // where this head's key starts in a cached key row
     const int qpos_last = tile.qpos0 + tile.n_rows - 1;
-    const int first_key = window > 0 ? max(0, tile.qpos0 - window + 1) : 0;
+    const int first_key = mask.chunk > 0 ? tile.qpos0 - tile.qpos0 % mask.chunk : (window > 0 ? max(0, tile.qpos0 - window + 1) : 0);
     const int block_first = first_key / BN;
-    const int n_blocks = qpos_last / BN - block_first + 1;
+    const int keep = window > 0 ? mask.keep_first : 0;
+    const int keep_blocks = keep > 0 ? min((keep + BN - 1) / BN, block_first) : 0;     // blocks of kept first keys below the window's
+    const int n_blocks = keep_blocks + qpos_last / BN - block_first + 1;
+    auto block_of = [&](int j) { return j < keep_blocks ? j : block_first + j - keep_blocks; };
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -144,7 +155,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 if (c < n_kc) tma_load_2d(q_smem + c * BM * KC * 2, &map_q, q_full, head * dh + c * KC, tile.row_start);
             const int32_t* pages = page_table + (size_t)tile.slot * max_pages;
             auto tile_row = [&](int j) {
-                int page = pages[block_first + j];
+                int page = pages[block_of(j)];
                 if (page < 0) { atomicExch(status, 3); page = 0; }       // still fill the stage so nobody waits for it
                 return (page * n_kv_heads + kvh) * BN;
             };
@@ -156,7 +167,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 mbar_expect_tx(&k_full[st], BN * KC * 2 * n_kc);
 #pragma unroll
                 for (int c = 0; c < NKC; ++c)
-                    if (c < n_kc) tma_load_2d(k_tile + c * BN * KC * 2, &map_k, &k_full[st], c * KC, row);
+                    if (c < n_kc) tma_load_2d(k_tile + c * BN * KC * 2, &map_k, &k_full[st], key_col + c * KC, row);
                 return true;
             };
             auto load_v = [&](int j) -> bool {
@@ -246,7 +257,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const int r = quad * 32 + lane;
         const bool valid = r < tile.n_rows;
         const int qpos = valid ? tile.qpos0 + r : -1;
-        const int lo = (window > 0 && valid) ? max(0, qpos - window + 1) : 0;
+        const int lo = !valid ? 0 : mask.chunk > 0 ? qpos - qpos % mask.chunk : window > 0 ? max(0, qpos - window + 1) : 0;
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
         float m = -INFINITY, l = 0.f;
         bool ok = true;
@@ -258,8 +269,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             uint32_t raw[32];
             tmem_load_32x32(tmem_base + lane_base + (uint32_t)((j & 1) * BN + half * 32), raw);
             tmem_load_wait();
-            const int key0 = (block_first + j) * BN + half * 32;
-            const bool all_visible = key0 + 31 <= qpos && key0 >= lo;
+            const int key0 = block_of(j) * BN + half * 32;
+            const bool all_visible = key0 + 31 <= qpos && (key0 >= lo || key0 + 31 < keep);
             if (cap_log2 > 0.f) {                    // the capped scores, already in log2 units (`sl2` is then 1)
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
@@ -272,7 +283,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
                     const int key = key0 + c;
-                    if (key > qpos || key < lo) raw[c] = 0xff800000u;       // -inf
+                    if (key > qpos || (key < lo && key >= keep)) raw[c] = 0xff800000u;       // -inf
                 }
             }
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -348,11 +359,15 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
         lsum[half * BM + r] = l;
         asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
-        const float l_all = lsum[r] + lsum[BM + r];
+        float l_all = lsum[r] + lsum[BM + r];
+        // the sink: one more term of the softmax's sum, in the units of the row's maximum (log2, scaled); both of the
+        // row's threads hold the same m
+        if (mask.sink && m != -INFINITY) l_all += exp2f(mask.sink[head] * 1.4426950408889634f - m);
         if (ok && !*aborted) {
             tc_fence_after_sync();
             const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
             __nv_bfloat16* orow = out + (size_t)(tile.row_start + r) * ldo + (size_t)head * dv;
+            float* orow32 = reinterpret_cast<float*>(out) + (size_t)(tile.row_start + r) * ldo + (size_t)head * dv;
             const __nv_bfloat16* grow = gate ? gate + (size_t)(tile.row_start + r) * ldg + (size_t)head * dv : nullptr;
             for (int c = half; c * 32 < dv; c += 2) {
                 uint32_t o[32];
@@ -361,7 +376,15 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 if (valid) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
-                        if (c * 32 + i < dv) {
+                        if (c * 32 + i < dv && mask.out_f32) {          // 32-bit results: no gate on this path
+                            float4 lo4, hi4;
+                            lo4.x = __uint_as_float(o[i]) * inv; lo4.y = __uint_as_float(o[i + 1]) * inv;
+                            lo4.z = __uint_as_float(o[i + 2]) * inv; lo4.w = __uint_as_float(o[i + 3]) * inv;
+                            hi4.x = __uint_as_float(o[i + 4]) * inv; hi4.y = __uint_as_float(o[i + 5]) * inv;
+                            hi4.z = __uint_as_float(o[i + 6]) * inv; hi4.w = __uint_as_float(o[i + 7]) * inv;
+                            *reinterpret_cast<float4*>(orow32 + c * 32 + i) = lo4;
+                            *reinterpret_cast<float4*>(orow32 + c * 32 + i + 4) = hi4;
+                        } else if (c * 32 + i < dv) {
                             uint32_t w[4];
                             float g8[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
                             if (grow) {
@@ -432,7 +455,7 @@ template <int NKC>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, long long ldo,
            const TileInfo* tiles, int n_tiles, const int32_t* page_table, int max_pages, int n_heads, int n_kv_heads,
            int dh, float scale_log2, int window, int32_t* status, int dv, float cap_log2, float cap_k2, const void* gate,
-           long long ldg, cudaStream_t stream) {
+           long long ldg, const MaskOpts& mask, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<NKC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -443,7 +466,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     }
     attention_prefill_kernel<NKC><<<dim3(n_heads, n_tiles), THREADS, smem_bytes<NKC>(), stream>>>(
         mq, mk, mv, (__nv_bfloat16*)out, (size_t)ldo, tiles, page_table, max_pages, n_heads, n_kv_heads, dh,
-        scale_log2, window, status, dv, cap_log2, cap_k2, (const __nv_bfloat16*)gate, (size_t)ldg);
+        scale_log2, window, status, dv, cap_log2, cap_k2, (const __nv_bfloat16*)gate, (size_t)ldg, mask);
     return qs_check_launch("attention_prefill");
 }
 
@@ -457,13 +480,25 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
 // The general form: values with a head size `dv` of their own (V [n_pages][n_kv_heads][64][dv], out [T, n_heads * dv]),
 // scores capped as softcap tanh(s / softcap) when softcap > 0, and an optional sigmoid gate [T, n_heads * dv]
 // (bfloat16, row stride ldg, 16-byte aligned rows) on the output.
-QS_API int qs_attention_prefill_ex(void* out, long long ldo, const void* q, long long ldq, int T_tokens,
-                                   const void* k_cache, const void* v_cache, int n_pages,
-                                   const int32_t* page_table, int max_pages, int page_tokens,
-                                   const int32_t* tiles, int n_tiles, int n_heads, int n_kv_heads, int dh,
-                                   float scale, int window, int32_t* status, int dv, float softcap, const void* gate,
-                                   long long ldg, cudaStream_t stream) {
+//
+// The masked form adds: `chunk` c > 0 (without a window): a query sees the keys of its own chunk of c positions counted
+// from 0; `keep_first` n (with a window): the sequence's first n keys stay visible; `sink` (float32 [n_heads], may be
+// null): exp(sink_h) joins each softmax's sum without key or value; `maps` m > 1: K is [n_pages][n_kv_heads][64][m * dh]
+// and n_heads counts m query heads per head, query head j reading key j % m; `out_f32`: out is float32 (ldo in floats,
+// rows 16-byte aligned), which excludes a gate.
+QS_API int qs_attention_prefill_masked(void* out, long long ldo, const void* q, long long ldq, int T_tokens,
+                                       const void* k_cache, const void* v_cache, int n_pages,
+                                       const int32_t* page_table, int max_pages, int page_tokens,
+                                       const int32_t* tiles, int n_tiles, int n_heads, int n_kv_heads, int dh,
+                                       float scale, int window, int32_t* status, int dv, float softcap, const void* gate,
+                                       long long ldg, int chunk, int keep_first, const float* sink, int maps, int out_f32,
+                                       cudaStream_t stream) {
     if (n_tiles == 0 || T_tokens == 0) return QS_OK;
+    if (maps < 1) maps = 1;
+    QS_REQUIRE(chunk >= 0 && keep_first >= 0 && !(chunk > 0 && window > 0), "attention_prefill: a window of %d and chunks of %d", window, chunk);
+    QS_REQUIRE(n_heads % maps == 0 && (n_heads / maps) % n_kv_heads == 0, "attention_prefill: %d query heads in %d maps over %d key heads",
+               n_heads, maps, n_kv_heads);
+    QS_REQUIRE(!out_f32 || (!gate && ldo % 4 == 0), "attention_prefill: 32-bit results take no gate and rows of whole 16 bytes");
     QS_REQUIRE(dv % 16 == 0 && dv >= 16 && dv <= 256, "attention_prefill: value head size %d must be a multiple of 16 up to 256", dv);
     QS_REQUIRE(!gate || (ldg % 8 == 0 && ((uintptr_t)gate % 16) == 0), "attention_prefill: the gate's rows must be 16-byte aligned");
     QS_REQUIRE(scale > 0.f && softcap >= 0.f, "attention_prefill: the scale must be positive and the cap not negative");
@@ -478,21 +513,33 @@ QS_API int qs_attention_prefill_ex(void* out, long long ldo, const void* q, long
     int rc;
     if ((rc = make_map(&mq, q, T_tokens, (long long)n_heads * dh, ldq, BM)) != QS_OK) return rc;
     const long long kv_rows = (long long)n_pages * n_kv_heads * BN;
-    if ((rc = make_map(&mk, k_cache, kv_rows, dh, dh, BN)) != QS_OK) return rc;
+    if ((rc = make_map(&mk, k_cache, kv_rows, (long long)maps * dh, (long long)maps * dh, BN)) != QS_OK) return rc;
     if ((rc = make_map(&mv, v_cache, kv_rows, dv, dv, BN)) != QS_OK) return rc;
     const float log2e = 1.4426950408889634f;
     const float scale_log2 = scale * log2e;
     const float cap_log2 = softcap > 0.f ? softcap * log2e : 0.f;
     const float cap_k2 = softcap > 0.f ? 2.0f * log2e * scale / softcap : 0.f;
     const TileInfo* ti = reinterpret_cast<const TileInfo*>(tiles);
+    const MaskOpts mask = {chunk, keep_first, maps, out_f32, sink};
     const int nkc = ((dh > dv ? dh : dv) + KC - 1) / KC;
 #define GO(NKC) return launch<NKC>(mq, mk, mv, out, ldo, ti, n_tiles, page_table, max_pages, n_heads, n_kv_heads, dh, \
-                                   scale_log2, window, status, dv, cap_log2, cap_k2, gate, ldg, stream)
+                                   scale_log2, window, status, dv, cap_log2, cap_k2, gate, ldg, mask, stream)
     if (nkc == 1) GO(1);
     if (nkc == 2) GO(2);
     if (nkc == 3) GO(3);
     GO(4);
 #undef GO
+}
+
+QS_API int qs_attention_prefill_ex(void* out, long long ldo, const void* q, long long ldq, int T_tokens,
+                                   const void* k_cache, const void* v_cache, int n_pages,
+                                   const int32_t* page_table, int max_pages, int page_tokens,
+                                   const int32_t* tiles, int n_tiles, int n_heads, int n_kv_heads, int dh,
+                                   float scale, int window, int32_t* status, int dv, float softcap, const void* gate,
+                                   long long ldg, cudaStream_t stream) {
+    return qs_attention_prefill_masked(out, ldo, q, ldq, T_tokens, k_cache, v_cache, n_pages, page_table, max_pages, page_tokens,
+                                       tiles, n_tiles, n_heads, n_kv_heads, dh, scale, window, status, dv, softcap, gate, ldg,
+                                       0, 0, nullptr, 1, 0, stream);
 }
 
 QS_API int qs_attention_prefill(void* out, long long ldo, const void* q, long long ldq, int T_tokens,

@@ -1,7 +1,8 @@
 """Prefill and decode throughput of a Lutelorn model beside a GPT-J model of equal size, and the kernels that
 Lutelorn adds, each against its roofline (`bench.py --design lutelorn`); the same for a Fofinex model beside a
 Lutelorn model, the library's closest design (a 32-bit stream, matrix-state mixers among attention layers), with
-the kernels that Fofinex adds (`bench.py --design fofinex`).
+the kernels that Fofinex adds (`bench.py --design fofinex`); and for a Sefuvik model beside a Lutelorn model
+(`bench.py --design sefuvik`).
 
 Sizes resemble a real model's layers: a width, heads of 128 (attention: a quarter as many key heads), a gated
 feed-forward of 8/3 width on every layer, the mixers in the order lightning, attention, lightning, wkv; the
@@ -57,6 +58,32 @@ def fofinex_config(width: int, layers: int) -> dict:
             mixer["kv_from"] = i - 2                    # every second latent layer reads the latents of the one before
         out.append({"type": kind, "mixer": mixer, "mlp": dense if i % 2 == 0 else routed})
     return {"architecture": "Fofinex", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-5}, "layers": out, "max_positions": 8192}
+
+
+def sefuvik_config(width: int, layers: int) -> dict:
+    """Heads of 128; the residual stream in four copies; mixers in the order retention, pair (attention in chunks of
+    512 with sinks beside the gated delta rule with four taps and bottlenecks of 64), retention, differential attention
+    (half as many heads, each with two maps of 128 and values of 256; a window of 1,024 that keeps the first four
+    tokens); a gated feed-forward of 8/3 width on every layer."""
+    heads = width // 128
+    mlp = {"kind": "dense", "ff": (width * 8 // 3 + 255) // 256 * 256}
+    decay = [1.0 - 2.0 ** (-5.0 - 5.0 * i / max(heads - 1, 1)) for i in range(heads)]
+    kinds = {
+        "retention": {"type": "retention", "mlp": mlp,
+                      "mixer": {"heads": heads, "dim": 128, "vdim": 128, "decay": decay, "rot": {"dims": 64, "base": 10000.0}}},
+        "parallel": {"type": "parallel", "mlp": mlp, "mixer": {
+            "left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "rot": {"dims": 64, "base": 10000.0},
+                     "scale": 128 ** -0.5, "mask": {"size": 512}},
+            "right": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64,
+                      "gate_rank": 64},
+            "left_scale": 0.5, "right_scale": 0.5}},
+        "attention": {"type": "attention", "mlp": mlp,
+                      "mixer": {"heads": heads // 2, "kv_heads": max(1, heads // 8), "dim": 128, "vdim": 256, "scale": 128 ** -0.5,
+                                "diff": 0.3, "mask": {"size": 1024, "keep_first": 4}}},
+    }
+    order = ["retention", "parallel", "retention", "attention"]
+    return {"architecture": "Sefuvik", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-5}, "streams": 4,
+            "layers": [kinds[order[i % 4]] for i in range(layers)], "max_positions": 8192}
 
 
 def gptj_config(width: int, layers: int) -> dict:
@@ -359,6 +386,126 @@ def kernel_table_fofinex(torch, np, pk, width=2048, T=4096, batch=32, ctx=2048):
     return rows
 
 
+def kernel_table_sefuvik(torch, np, pk, width=2048, T=4096, batch=32, ctx=2048):
+    """The kernels that Sefuvik adds, each by itself beside the like kernel of the Lutelorn parts: milliseconds and the
+    fraction of its roofline."""
+    from .csrc import attention_bf16, ops
+    from .parts.recurrent import CHUNK_TOKENS
+    from .parts.rotary import _table
+    t = Timer(torch)
+    bf, f32 = torch.bfloat16, torch.float32
+    dev = "cuda"
+    H, d, S = width // 128, 128, 4
+    G = max(1, H // 4)
+    hbm, tens = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    fp32 = 2.0 * FP32_LANES_PER_SM * SMS * pk.get("sm_max_mhz", 1965.0) * 1e6
+    rows = []
+
+    def add(name, like, ms, nbytes=0, flops=0, bound="hbm"):
+        peak = {"hbm": hbm, "tensor": tens, "fp32": fp32}[bound]
+        done = (nbytes if bound == "hbm" else flops) / (ms * 1e-3)
+        rows.append({"kernel": name, "like": like, "ms": round(ms, 4), "bound": bound, "frac": round(done / peak, 4)})
+
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=dev)          # noqa: E731
+    # the stream in four copies: a sublayer's write, the next one's read and its norm in one pass
+    mix, w_in, w_out = torch.randn(S, S, device=dev), torch.randn(S, device=dev), torch.randn(S, device=dev)
+    for n_rows, tag in ((T, "prompt"), (batch, "decode")):
+        xs, y = torch.randn(n_rows, S * width, device=dev), torch.randn(n_rows, width, device=dev)
+        x1, w, ls = torch.randn(n_rows, width, device=dev), torch.randn(width, device=dev, dtype=bf), torch.randn(width, device=dev, dtype=bf)
+        add(f"stream of {S} copies: write + read + norm {tag}", "rmsnorm + update",
+            t.kernel(lambda: ops.hyper_mix_norm(xs, S, width, y=y, layer_scale=ls, mix=mix, out_weights=w_out, in_weights=w_in,
+                                                norm_weight=w, offset=1.0, eps=1e-5, out_dtype=bf)), n_rows * width * (8 * S + 6))
+        add(f"rmsnorm + update {tag} (Lutelorn)", "", t.kernel(lambda: ops.rmsnorm(x1, w, 1e-6, 1.0, out_dtype=bf, update=y, mult=0.0)),
+            n_rows * width * 14)
+    # attention in chunks with sinks (grouped keys), and differential attention in a window that keeps first tokens
+    n_pages = batch * ctx // 64
+    table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(batch, ctx // 64)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    tl = min(T, ctx)
+    pslot, ppos = i32([0] * tl), i32(list(range(tl)))
+    dslot, dpos = i32(list(range(batch))), i32([ctx - 1] * batch)
+    tiles = torch.tensor([(s0, min(128, tl - s0), s0, 0) for s0 in range(0, tl, 128)][::-1], dtype=torch.int32, device=dev)
+    kg, vg = (torch.randn(n_pages, G, 64, d, device=dev, dtype=bf) for _ in range(2))
+    q = torch.randn(tl, H * d, device=dev, dtype=bf)
+    sink = torch.randn(H, device=dev)
+    chunk = 512
+    seen = sum(p % chunk + 1 for p in range(tl))
+    ms = t.kernel(lambda: ops.attention(q, H, G, d, d ** -0.5, 0, pslot, ppos, table, 64, kg, vg, status, chunk=chunk, sink=sink))
+    add(f"attention in chunks of {chunk} with sinks, prompt {tl}", "attention prompt", ms, flops=4.0 * H * d * seen, bound="tensor")
+    qd = q[:batch].contiguous()
+    ms = t.kernel(lambda: ops.attention(qd, H, G, d, d ** -0.5, 0, dslot, dpos, table, 64, kg, vg, status, chunk=chunk, sink=sink))
+    add(f"attention in chunks of {chunk} with sinks, decode {batch} x {ctx}", "attention decode", ms,
+        batch * ((ctx - 1) % chunk + 1) * G * d * 4)
+    H2, G2, dv2, window, keep = H // 2, max(1, H // 8), 256, 1024, 4
+    k2 = torch.randn(n_pages, G2, 64, 2 * d, device=dev, dtype=bf)
+    v2 = torch.randn(n_pages, G2, 64, dv2, device=dev, dtype=bf)
+    q2 = torch.randn(tl, H2 * 2 * d, device=dev, dtype=bf)
+    seen = sum(min(p + 1, window + keep) for p in range(tl))
+    ms = t.kernel(lambda: ops.attention(q2, H2 * 2, G2, d, d ** -0.5, window, pslot, ppos, table, 64, k2, v2, status, v_head_dim=dv2,
+                                        keep_first=keep, maps=2, out_dtype=f32))
+    add(f"two maps in a window of {window} + {keep}, prompt {tl}", "attention prompt", ms, flops=2.0 * 2 * H2 * (d + dv2) * seen, bound="tensor")
+    q2d = q2[:batch].contiguous()
+    ms = t.kernel(lambda: ops.attention(q2d, H2 * 2, G2, d, d ** -0.5, window, dslot, dpos, table, 64, k2, v2, status, v_head_dim=dv2,
+                                        keep_first=keep, maps=2, out_dtype=f32))
+    add(f"two maps in a window of {window} + {keep}, decode {batch} x {ctx}", "attention decode", ms,
+        batch * (window + keep) * G2 * (2 * d + dv2) * 2)
+    ms = t.kernel(lambda: attention_bf16.prefill(q, H, G, d, d ** -0.5, 0, tiles, table, 64, kg, vg, status))
+    add(f"attention prompt {tl}, {G} key heads (Lutelorn's sizes)", "", ms, flops=4.0 * H * d * tl * tl / 2, bound="tensor")
+    ms = t.kernel(lambda: attention_bf16.decode(qd, H, G, d, d ** -0.5, 0, dslot, dpos, table, 64, kg, vg, ctx, status))
+    add(f"attention decode {batch} x {ctx}, {G} key heads (Lutelorn's sizes)", "", ms, batch * ctx * G * d * 4)
+    for n_rows, tag in ((T, "prompt"), (batch, "decode")):
+        a2 = torch.randn(n_rows, H2 * 2 * dv2, device=dev)
+        add(f"difference of the maps, unit norm {tag}", "gated group norm",
+            t.kernel(lambda: ops.pair_diff_norm(a2, H2, dv2, 0.4, 0.7, 1e-5, bf)), n_rows * H2 * dv2 * 10)
+        og, g = torch.randn(n_rows, width, device=dev), torch.randn(n_rows, width, device=dev, dtype=bf)
+        wn = torch.randn(width, device=dev, dtype=bf)
+        add(f"gated group norm {tag} (Lutelorn)", "", t.kernel(lambda: ops.gated_group_norm(og, width, wn, g, "sigmoid", 1e-6, bf)),
+            n_rows * width * 8)
+    # retention: q and k leave their product in 32-bit and are rotated in 32-bit; the scan is Lutelorn's
+    table_r = _table(64, 10000.0, 8192, dev)
+    for n_rows, tag, slot, pos in ((T, "prompt", i32([0] * T), i32(list(range(T)))), (batch, "decode", dslot, dpos)):
+        qr = torch.randn(n_rows, H * d, device=dev)
+        add(f"rotation of q or k in 32-bit {tag}", "(in attention's cache write)",
+            t.kernel(lambda: ops.rope_store(qr, None, None, H, 0, d, 64, table_r, slot, pos, None, 64, None, None, status, settled=True,
+                                            half_layout=True)), n_rows * H * d * 8)
+    # the gated delta rule: preparation, the convolutions' state, the scan in order
+    Gq, taps, nq, nv = max(1, H // 2), 4, max(1, H // 2) * d, H * d
+    conv = [torch.randn(n, taps, device=dev, dtype=bf) for n in (nq, nq, nv)]
+    held = torch.zeros(batch, taps - 1, 2 * nq + nv, device=dev, dtype=bf)
+    a_log = torch.full((H,), -3.0, device=dev)
+    n_chunks = T // CHUNK_TOKENS
+    chunks = (i32(list(range(0, T + 1, CHUNK_TOKENS))), i32(list(range(n_chunks))), i32([0, n_chunks]), n_chunks)
+    one_start, one_slot = i32([0, T]), i32([0])
+    dec_start, dec_slot = i32(list(range(batch + 1))), i32(list(range(batch)))
+    state = torch.zeros(batch, H, d, d, device=dev)
+    for n_rows, tag, slot, pos, starts, slots, n_seq in ((T, "prompt", i32([0] * T), i32(list(range(T))), one_start, one_slot, 1),
+                                                         (batch, "decode", dslot, dpos, dec_start, dec_slot, batch)):
+        p = torch.randn(n_rows, 2 * nq + nv, device=dev, dtype=bf)
+        qq, kk, vv = p[:, :nq], p[:, nq:2 * nq], p[:, 2 * nq:]
+        a, b = torch.randn(n_rows, H * d, device=dev), torch.randn(n_rows, H, device=dev)
+        add(f"delta rule: convolutions, unit vectors, decays {tag}", "token shift",
+            t.kernel(lambda: ops.delta_prepare(qq, kk, vv, *conv, held, a, b, a_log, slot, pos, Gq, H, d, d, d ** -0.5, 1e-6)),
+            n_rows * ((2 * nq + nv) * 6 + H * d * 8 + H * 8))
+        add(f"delta rule: the convolutions' state {tag}", "(none)",
+            t.kernel(lambda: ops.conv_state_update(held, qq, kk, vv, nq, nv, taps, starts, slots, n_seq)), n_seq * (taps - 1) * (2 * nq + nv) * 4)
+        qo, ko, vo, decay, beta = ops.delta_prepare(qq, kk, vv, *conv, held, a, b, a_log, slot, pos, Gq, H, d, d, d ** -0.5, 1e-6)
+        ms = t.kernel(lambda: ops.state_scan("delta", qo, ko, vo, state, starts, slots, n_seq, H, d, d, key_decay=decay, token_weight=beta,
+                                             qk_group=H // Gq), repeats=5)
+        if tag == "prompt":                             # decay, S^T k, the write and the read-out: 4 multiply-adds per element and token
+            add(f"state scan delta prompt {T} (in order)", "state scan decay prompt", ms, flops=8.0 * T * H * d * d, bound="fp32")
+        else:
+            add(f"state scan delta decode {batch}", "state scan decay decode", ms, 2 * state.numel() * 4)
+    ql, kl, vl = (torch.randn(T, H * d, device=dev, dtype=bf) for _ in range(3))
+    dec = torch.full((H,), 0.99, device=dev)
+    ms = t.kernel(lambda: ops.state_scan("decay", ql, kl, vl, state, one_start, one_slot, 1, H, d, d, head_decay=dec, chunks=chunks))
+    add(f"state scan decay prompt {T} (Lutelorn)", "", ms, flops=6.0 * T * H * d * d, bound="fp32")
+    ms = t.kernel(lambda: ops.state_scan("decay", ql[:batch], kl[:batch], vl[:batch], state, dec_start, dec_slot, batch, H, d, d, head_decay=dec))
+    add(f"state scan decay decode {batch} (Lutelorn)", "", ms, 2 * state.numel() * 4)
+    xb, mu, last = torch.randn(T, width, device=dev, dtype=bf), torch.rand(5, width, device=dev), torch.zeros(batch, width, device=dev, dtype=bf)
+    add("token shift prompt (Lutelorn)", "", t.kernel(lambda: ops.token_shift(xb, mu, last, i32([0] * T), i32(list(range(T))))), T * width * 12)
+    return rows
+
+
 def run_fofinex(args, pk) -> int:
     import numpy as np
     import torch
@@ -380,9 +527,32 @@ def run_fofinex(args, pk) -> int:
     return 0
 
 
+def run_sefuvik(args, pk) -> int:
+    import numpy as np
+    import torch
+    import qstream_b200 as qs
+    out = {"impl": "ours", "design": "sefuvik", "beside": "lutelorn", "dtype": "bf16", "data": "synthetic token ids, random weights",
+           "peaks": {k: pk[k] for k in ("hbm_gbs", "bf16_tflops", "source")}, "sizes": {}}
+    for name, size in SIZES.items():
+        entry = {}
+        for which, cfg in (("sefuvik", sefuvik_config(**size)), ("lutelorn", lutelorn_config(**size))):
+            model = qs.CausalLM.random(qs.config_from_dict(cfg), seed=0, dtype="bfloat16", device="cuda:0")
+            r = model_throughput(qs, torch, np, model, VOCAB, 2048, 8, 1024, min(args.steps, 32), max(3, min(args.warmup, 4)))
+            r["weights_mb"] = round(model.weight_bytes / 2**20, 1)
+            entry[which] = r
+            del model
+            torch.cuda.empty_cache()
+        out["sizes"][name] = entry
+    out["kernels"] = kernel_table_sefuvik(torch, np, pk)
+    print(json.dumps(out))
+    return 0
+
+
 def run(args, pk) -> int:
     if getattr(args, "design", "") == "fofinex":
         return run_fofinex(args, pk)
+    if getattr(args, "design", "") == "sefuvik":
+        return run_sefuvik(args, pk)
     import numpy as np
     import torch
     import qstream_b200 as qs

@@ -165,14 +165,23 @@ class Attention(Mixer):
         return self._attend_masked(q, step, view, out, gate)
 
     def _attend_masked(self, q, step, view, out, gate):
-        """Chunks, kept first tokens, sinks and pairs of maps: the generic kernel, every softmax in 32-bit; the two maps'
-        results stay in 32-bit until their difference has been normed."""
+        """Chunks, kept first tokens, sinks and pairs of maps: the bfloat16 engine's decode and prefill kernels take
+        them as options (the gate in their last stage), every other case goes to the generic kernel; every softmax
+        in 32-bit; the two maps' results stay in 32-bit until their difference has been normed."""
         s, b = self.spec, step.batch
         two = self.maps == 2
-        o = ops.attention(q, s.n_heads * self.maps, s.n_kv_heads, s.head_dim, s.scale, s.window, b.tok_slot, b.tok_pos,
-                          view.page_table, view.page_tokens, view.k, view.v, step.status, out=None if two or gate is not None else out,
-                          v_head_dim=s.value_dim, softcap=s.softcap, chunk=self.chunk, keep_first=self.keep_first,
-                          sink=self.sink, maps=self.maps, out_dtype=torch.float32 if two else None)
+        wide = torch.float32 if two else None
+        o = None
+        if q.dtype == torch.bfloat16:
+            from ..csrc import attention_bf16
+            o = attention_bf16.attend(q, s, step, view, None if two else out, gate, sink=self.sink, out_dtype=wide)
+            if o is not None:
+                gate = None                                 # applied by the kernel
+        if o is None:
+            o = ops.attention(q, s.n_heads * self.maps, s.n_kv_heads, s.head_dim, s.scale, s.window, b.tok_slot, b.tok_pos,
+                              view.page_table, view.page_tokens, view.k, view.v, step.status, out=None if two or gate is not None else out,
+                              v_head_dim=s.value_dim, softcap=s.softcap, chunk=self.chunk, keep_first=self.keep_first,
+                              sink=self.sink, maps=self.maps, out_dtype=wide)
         if two:
             o = ops.pair_diff_norm(o, s.n_heads, s.value_dim, self.lam, 1.0 - float(s.diff), float(s.eps), q.dtype)
         if gate is not None:

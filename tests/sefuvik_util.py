@@ -187,9 +187,9 @@ def logits_error(got, ref):
 # float32: rounding of 32-bit sums and exponentials only, doubled by every layer of these large weights (typical rows
 # are off by 5e-6, single ones by 3e-4); a structural fault moves the rows it touches by 3e-2 at least.  bfloat16 (with
 # the gentler weights): a single row may be off by a quarter of its spread, a request's rows (where there are enough of them
-# for a median to mean something) by 3 % in the median.
+# for a median to mean something) by 5 % in the median.
 F32_LIMIT = 1e-3
-BF16_ROW_LIMIT, BF16_MEDIAN_LIMIT = 2.5e-1, 3e-2
+BF16_ROW_LIMIT, BF16_MEDIAN_LIMIT = 2.5e-1, 5e-2
 
 
 def assert_close(got, ref, dtype, what=""):

@@ -97,7 +97,7 @@ class Pages:
         # values past the sequence's end, in its last page, are read by no one but must be numbers
         self.v[order[-1], :, T % page_tokens or page_tokens:] = 0
         self.k[order[-1], :, T % page_tokens or page_tokens:] = 0
-        self.table = i32(np.concatenate([order, [-1, -1]])[None, :])
+        self.table = i32(np.concatenate([order, [-1] * 4])[None, :])
         self.page_tokens = page_tokens
         self.status = torch.zeros(1, dtype=torch.int32, device=DEV)
 
@@ -229,3 +229,51 @@ def test_the_gated_delta_rule_step_after_step(sizes):
         assert g.shape == want[i].shape
         np.testing.assert_allclose(g, want[i], rtol=0, atol=1e-4 * max(1.0, np.abs(want[i]).max()))
     assert float(state[1].abs().max()) == 0.0 and float(state[3].abs().max()) == 0.0    # the other slots were not touched
+
+
+def rbf(a):
+    """Rounded to bfloat16, as float64."""
+    return torch.tensor(np.asarray(a), dtype=torch.bfloat16).to(torch.float64).numpy()
+
+
+@pytest.mark.parametrize("mask", MASKS, ids=lambda m: "-".join(f"{k}{v}" for k, v in m.items()))
+@pytest.mark.parametrize("sizes", [(4, 2, 16, 32), (2, 2, 64, 32), (4, 1, 128, 128), (2, 1, 128, 256)])
+def test_the_bfloat16_kernels_take_the_same_masks(mask, sizes):
+    """The tensor-core kernel for prompts (whole, and as a second portion that starts in the middle of a page) and the
+    split-key kernel for single queries, with a gate where the form has one map; 330 keys, so that queries lie beyond
+    the first split of 256 keys and windows leave whole pages (and splits) behind."""
+    from qstream_b200.csrc import attention_bf16
+    H, G, d, dv = sizes
+    chunk, window, keep = mask.get("chunk", 0), mask.get("window", 0), mask.get("keep", 0)
+    maps = mask.get("maps", 1)
+    rng = np.random.default_rng(H * d + chunk + window + 1)
+    T, scale = 330, 2.0 / math.sqrt(d)
+    q = rbf(rng.normal(size=(T, H, maps, d)))
+    k = rbf(rng.normal(size=(T, G, maps, d)))
+    v = rbf(rng.normal(size=(T, G, dv)))
+    sink = r32(rng.normal(2.0, 2.0, H)) if mask.get("sink") else None
+    gate = rbf(rng.normal(size=(T, H * dv))) if maps == 1 else None
+    see = (lambda i, j: P.visible_chunk(i, j, chunk)) if chunk else (lambda i, j: P.visible_window(i, j, window, keep))
+    want = np.stack([P.masked_softmax_attention(q[:, :, m], k[:, :, m], v, scale, see, sink=sink) for m in range(maps)], axis=2)
+    want = want.reshape(T, H * maps * dv)
+    if gate is not None:
+        want = want * P.sigmoid(gate)
+    pages = Pages(k.reshape(T, G, maps * d), v, dtype=torch.bfloat16)
+    bf = torch.bfloat16
+    qd = dev(q.reshape(T, H * maps * d), bf)
+    gd = dev(gate, bf) if gate is not None else None
+    opts = dict(v_head_dim=dv, chunk=chunk, keep_first=keep, sink=dev(sink) if sink is not None else None, maps=maps,
+                out_dtype=torch.float32 if maps > 1 else None)
+    for start in (0, 100):
+        rows = T - start
+        tiles = i32([(a - start, min(128, T - a), a, 0) for a in range(start, T, 128)][::-1])
+        got = attention_bf16.prefill(qd[start:], H * maps, G, d, scale, window, tiles, pages.table, 64, pages.k, pages.v, pages.status,
+                                     gate=gd[start:] if gd is not None else None, **opts)
+        assert got.dtype == (torch.float32 if maps > 1 else bf) and got.shape[0] == rows
+        np.testing.assert_allclose(got.float().cpu().numpy(), want[start:], rtol=0, atol=3e-2)
+    places = np.array([0, 1, 63, 64, 65, 127, 128, 255, 256, 257, 300, 329])
+    got = attention_bf16.decode(qd[places].contiguous(), H * maps, G, d, scale, window, i32(np.zeros(len(places))), i32(places),
+                                pages.table.expand(1, -1).contiguous(), 64, pages.k, pages.v, 512, pages.status,
+                                gate=gd[places].contiguous() if gd is not None else None, **opts)
+    np.testing.assert_allclose(got.float().cpu().numpy(), want[places], rtol=0, atol=1e-4 if maps > 1 else 1e-2)
+    assert int(pages.status.item()) == 0
