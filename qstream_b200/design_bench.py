@@ -430,23 +430,27 @@ def kernel_table_sefuvik(torch, np, pk, width=2048, T=4096, batch=32, ctx=2048):
     sink = torch.randn(H, device=dev)
     chunk = 512
     seen = sum(p % chunk + 1 for p in range(tl))
+    gate = torch.randn(tl, H * d, device=dev, dtype=bf)
+    ms = t.kernel(lambda: attention_bf16.prefill(q, H, G, d, d ** -0.5, 0, tiles, table, 64, kg, vg, status, chunk=chunk, sink=sink, gate=gate))
+    add(f"attention in chunks of {chunk} with sinks, gated, prompt {tl}", "attention prompt", ms, flops=4.0 * H * d * seen, bound="tensor")
     ms = t.kernel(lambda: ops.attention(q, H, G, d, d ** -0.5, 0, pslot, ppos, table, 64, kg, vg, status, chunk=chunk, sink=sink))
-    add(f"attention in chunks of {chunk} with sinks, prompt {tl}", "attention prompt", ms, flops=4.0 * H * d * seen, bound="tensor")
-    qd = q[:batch].contiguous()
-    ms = t.kernel(lambda: ops.attention(qd, H, G, d, d ** -0.5, 0, dslot, dpos, table, 64, kg, vg, status, chunk=chunk, sink=sink))
-    add(f"attention in chunks of {chunk} with sinks, decode {batch} x {ctx}", "attention decode", ms,
+    add(f"the same by the generic kernel (the 32-bit engine's), prompt {tl}", "", ms, flops=4.0 * H * d * seen, bound="fp32")
+    qd, gd = q[:batch].contiguous(), gate[:batch].contiguous()
+    ms = t.kernel(lambda: attention_bf16.decode(qd, H, G, d, d ** -0.5, 0, dslot, dpos, table, 64, kg, vg, ctx, status, chunk=chunk,
+                                                sink=sink, gate=gd))
+    add(f"attention in chunks of {chunk} with sinks, gated, decode {batch} x {ctx}", "attention decode", ms,
         batch * ((ctx - 1) % chunk + 1) * G * d * 4)
     H2, G2, dv2, window, keep = H // 2, max(1, H // 8), 256, 1024, 4
     k2 = torch.randn(n_pages, G2, 64, 2 * d, device=dev, dtype=bf)
     v2 = torch.randn(n_pages, G2, 64, dv2, device=dev, dtype=bf)
     q2 = torch.randn(tl, H2 * 2 * d, device=dev, dtype=bf)
     seen = sum(min(p + 1, window + keep) for p in range(tl))
-    ms = t.kernel(lambda: ops.attention(q2, H2 * 2, G2, d, d ** -0.5, window, pslot, ppos, table, 64, k2, v2, status, v_head_dim=dv2,
-                                        keep_first=keep, maps=2, out_dtype=f32))
+    ms = t.kernel(lambda: attention_bf16.prefill(q2, H2 * 2, G2, d, d ** -0.5, window, tiles, table, 64, k2, v2, status, v_head_dim=dv2,
+                                                 keep_first=keep, maps=2, out_dtype=f32))
     add(f"two maps in a window of {window} + {keep}, prompt {tl}", "attention prompt", ms, flops=2.0 * 2 * H2 * (d + dv2) * seen, bound="tensor")
     q2d = q2[:batch].contiguous()
-    ms = t.kernel(lambda: ops.attention(q2d, H2 * 2, G2, d, d ** -0.5, window, dslot, dpos, table, 64, k2, v2, status, v_head_dim=dv2,
-                                        keep_first=keep, maps=2, out_dtype=f32))
+    ms = t.kernel(lambda: attention_bf16.decode(q2d, H2 * 2, G2, d, d ** -0.5, window, dslot, dpos, table, 64, k2, v2, ctx, status,
+                                                v_head_dim=dv2, keep_first=keep, maps=2, out_dtype=f32))
     add(f"two maps in a window of {window} + {keep}, decode {batch} x {ctx}", "attention decode", ms,
         batch * (window + keep) * G2 * (2 * d + dv2) * 2)
     ms = t.kernel(lambda: attention_bf16.prefill(q, H, G, d, d ** -0.5, 0, tiles, table, 64, kg, vg, status))
