@@ -62,6 +62,8 @@ _SIGNATURES = {
                        c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
                        c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                        c_void_p, c_void_p, c_longlong, c_float, c_int, c_void_p], c_int),
+    "qs_delta_chunk_prefix": ([c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                               c_void_p], c_int),
     "qs_mlstm_gates": ([c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_float, c_void_p, c_longlong,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p], c_int),
     "qs_mlstm_output": ([c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int,
@@ -471,7 +473,7 @@ def keep_last_rows(dst: torch.Tensor, src: torch.Tensor, seq_start, seq_slot, n_
 
 def state_scan(mode: str, q, k, v, state, seq_start, seq_slot, n_seq, n_heads, key_dim, value_dim, head_decay=None,
                decay_logits=None, bonus=None, in_activation=None, chunks=None, token_decay=None, token_weight=None,
-               q_scale: float = 1.0, key_decay=None, qk_group: int = 1) -> torch.Tensor:
+               q_scale: float = 1.0, key_decay=None, qk_group: int = 1, want_output: bool = True) -> torch.Tensor:
     """Walk each sequence's tokens of this step through a per-head matrix state (float32 [slots, heads, value_dim,
     key_dim], updated in place); returns o [T, heads * value_dim] in float32.
     mode "decay": S <- decay_h S + k v^T, o = S^T q.  mode "wkv": o = (S + diag(bonus) k v^T)^T q, then
@@ -480,15 +482,21 @@ def state_scan(mode: str, q, k, v, state, seq_start, seq_slot, n_seq, n_heads, k
     a column of ones, whose state is the normaliser n <- a_t n + b_t k and whose output n.q is each head's last element.
     mode "delta": S' = diag(g_t) S, u = beta_t (v - S'^T k), S <- S' + k u^T, o = S^T q, with g = `key_decay` (float32
     [T, heads * key_dim]) and beta = `token_weight` (float32 [T, heads]); q and k hold heads / `qk_group` heads, head h
-    reading number h // qk_group; in order only (no chunks).  In mode "decay" `q_scale` multiplies q as well.
+    reading number h // qk_group.  With `chunks` the delta rule runs the same walk three times over the chunks side by
+    side (what a chunk does to an identity, what it writes from an empty state, and, once a prefix over the chunks has
+    given each its starting state, the chunk's outputs).  In mode "decay" `q_scale` multiplies q as well.
     `chunks` = (chunk_start, chunk_ids, seq_chunk, n_chunks), int32 device tensors: every sequence of the step cut
     into consecutive chunks (rows chunk_start[c] .. chunk_start[c + 1] of the packed batch; sequence s owns chunks
     seq_chunk[s] .. seq_chunk[s + 1]; chunk_ids = 0 .. n_chunks - 1).  The chunks then run side by side and a
     prefix over each sequence's chunks joins them; the result equals the walk in order up to 32-bit rounding."""
     T = q.shape[0]
-    o = torch.empty((T, n_heads * value_dim), dtype=torch.float32, device=q.device)
     if state.dtype != torch.float32 or state.stride(-1) != 1:
         raise QStreamError(QsError.INVALID_INPUT, "state_scan: the state must be float32")
+    if mode == "delta" and chunks is not None:
+        return _delta_in_chunks(q, k, v, state, seq_slot, n_seq, n_heads, key_dim, value_dim, key_decay, token_weight, qk_group, chunks)
+    o = torch.empty((T, n_heads * value_dim), dtype=torch.float32, device=q.device) if want_output else None
+    if v is None and mode != "delta":
+        raise QStreamError(QsError.INVALID_INPUT, "state_scan: only the delta rule walks without values")
     chunk_start = chunk_ids = seq_chunk = chunk_state = chunk_decay = None
     n_chunks = 0
     if chunks is not None:
@@ -498,12 +506,13 @@ def state_scan(mode: str, q, k, v, state, seq_start, seq_slot, n_seq, n_heads, k
     per_token = token_decay if token_decay is not None else token_weight
     if mode == "delta":
         decay_logits = key_decay
-        if chunks is not None or key_decay.dtype != torch.float32 or token_weight.dtype != torch.float32:
-            raise QStreamError(QsError.INVALID_INPUT, "state_scan: the delta rule walks in order over float32 decays and step sizes")
+        if key_decay.dtype != torch.float32 or token_weight.dtype != torch.float32:
+            raise QStreamError(QsError.INVALID_INPUT, "state_scan: the delta rule takes float32 decays and step sizes")
     if mode == "gated" and (token_decay.dtype != torch.float32 or token_decay.stride() != token_weight.stride()):
         raise QStreamError(QsError.INVALID_INPUT, "state_scan: the tokens' decays and weights must be float32 of one layout")
     check(library().qs_state_scan(
-        {"decay": 0, "wkv": 1, "gated": 2, "delta": 3}[mode], ptr(o), o.stride(0), ptr(q), q.stride(0), ptr(k), k.stride(0), ptr(v), v.stride(0),
+        {"decay": 0, "wkv": 1, "gated": 2, "delta": 3}[mode], ptr(o), o.stride(0) if o is not None else 0, ptr(q), q.stride(0),
+        ptr(k), k.stride(0), ptr(v), v.stride(0) if v is not None else 0,
         dtype_code(q), ptr(decay_logits), decay_logits.stride(0) if decay_logits is not None else 0, ptr(head_decay),
         ptr(bonus), _code(bonus), ptr(state), state.stride(0), _int32(seq_start, "seq_start"),
         _int32(seq_slot, "seq_slot"), int(n_seq), T, n_heads, key_dim, value_dim, ACTIVATIONS[in_activation],
@@ -511,6 +520,24 @@ def state_scan(mode: str, q, k, v, state, seq_start, seq_slot, n_seq, n_heads, k
         ptr(token_decay), ptr(token_weight), per_token.stride(0) if per_token is not None else 0, float(q_scale),
         int(qk_group), stream()))
     return o
+
+
+def _delta_in_chunks(q, k, v, state, seq_slot, n_seq, n_heads, key_dim, value_dim, key_decay, token_weight, qk_group, chunks):
+    """The delta rule of a long prompt, its chunks side by side.  A chunk acts on the state it starts from as
+    S <- P S + Q: P is what the chunk's walk (values of zero) makes of an identity, Q what it writes from an empty state;
+    `qs_delta_chunk_prefix` then gives every chunk its starting state and the slot its last one, and the walk runs once
+    more for the outputs.  The same arithmetic as the walk in order, regrouped; nothing is divided by a decay."""
+    chunk_start, chunk_ids, seq_chunk, n_chunks = chunks
+    dev = q.device
+    P = torch.eye(key_dim, dtype=torch.float32, device=dev).repeat(n_chunks, n_heads, 1, 1)
+    Q = torch.zeros((n_chunks, n_heads, value_dim, key_dim), dtype=torch.float32, device=dev)
+    walk = dict(key_decay=key_decay, token_weight=token_weight, qk_group=qk_group)
+    state_scan("delta", q, k, None, P, chunk_start, chunk_ids, n_chunks, n_heads, key_dim, key_dim, want_output=False, **walk)
+    state_scan("delta", q, k, v, Q, chunk_start, chunk_ids, n_chunks, n_heads, key_dim, value_dim, want_output=False, **walk)
+    start = torch.empty_like(Q)
+    check(library().qs_delta_chunk_prefix(ptr(P), ptr(Q), ptr(start), ptr(state), state.stride(0), _int32(seq_chunk, "seq_chunk"),
+                                          _int32(seq_slot, "seq_slot"), int(n_seq), n_heads, key_dim, value_dim, stream()))
+    return state_scan("delta", q, k, v, start, chunk_start, chunk_ids, n_chunks, n_heads, key_dim, value_dim, **walk)
 
 
 def delta_prepare(q, k, v, conv_q, conv_k, conv_v, conv_state, a, b, a_log, tok_slot, tok_pos, n_qk_heads, n_heads,

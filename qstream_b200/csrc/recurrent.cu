@@ -66,14 +66,14 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
     const int n_cols = min(cols, dv - col0);
     const int tid = threadIdx.x;
     // rows of the packed batch beyond the last sequence belong to nobody: give them a defined value
-    if (PHASE != 3 && s == 0) {
+    if (PHASE != 3 && s == 0 && (!DELTA || o)) {
         for (int t = seq_start[n_seq]; t < T_rows; ++t)
             for (int c = tid; c < n_cols; c += blockDim.x) o[(size_t)t * ldo + h * dv + col0 + c] = 0.f;
     }
     const int slot = seq_slot[s];
     const int t0 = seq_start[s], t1 = seq_start[s + 1];
     if (slot < 0) {
-        if (PHASE != 3)
+        if (PHASE != 3 && (!DELTA || o))
             for (int t = t0; t < t1; ++t)
                 for (int c = tid; c < n_cols; c += blockDim.x) o[(size_t)t * ldo + h * dv + col0 + c] = 0.f;
         return;
@@ -156,7 +156,7 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
         if (PHASE != 3) {
             for (int e = tid; e < nt * cols; e += blockDim.x) {
                 const int tt = e / cols, c = e - tt * cols;
-                sv[e] = c >= n_cols ? 0.f : (GATED && col0 + c == dvv) ? 1.0f
+                sv[e] = (c >= n_cols || (DELTA && !v)) ? 0.f : (GATED && col0 + c == dvv) ? 1.0f
                         : apply_activation(to_f32(v[(size_t)(base + tt) * ldv + h * dvv + col0 + c]), in_act);
             }
             if (GATED && tid < nt) sa[tid] = ga[(size_t)(base + tid) * ldg + h];
@@ -248,7 +248,7 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
                 acc1 += __shfl_xor_sync(0xffffffffu, acc1, off);
             }
             }
-            if (ks == 0) {
+            if (ks == 0 && (!DELTA || o)) {
                 // PHASE 3 adds to what PHASE 1 wrote: this thread is the element's only writer in this kernel, and a
                 // reduction that returns nothing does not make the loop wait for the old value
                 float* dst = o + (size_t)(base + tt) * ldo + h * dv + col0 + CPT * pair;
@@ -356,6 +356,76 @@ __global__ void token_shift_kernel(T* __restrict__ out, size_t ldo, size_t mix_s
         const float diff = (before ? to_f32(before[i]) : 0.f) - cur;
         for (int m = 0; m < n_mix; ++m)
             out[(size_t)m * mix_stride + (size_t)t * ldo + i] = from_f32<T>(fmaf(diff, mu[(size_t)m * D + i], cur));
+    }
+}
+
+// The delta rule over chunks that ran side by side.  A chunk's tokens act on the state as S <- P S + Q, with
+// P = A_n .. A_1 (A_t = (I - beta_t k_t k_t^T) diag(g_t), the same for every value column) and Q what the chunk
+// writes from an empty state; both come from the scan itself (P: the scan of an identity with values of zero).  This
+// kernel walks a sequence's chunks in order: it leaves in `start` the state each chunk starts from and in the slot the
+// state after the last.  Layouts as the state's: P [chunks][H][dk (column j)][dk (row i)], Q and start
+// [chunks][H][dv][dk].  A block owns DCB value columns of one head; nothing is divided by a decay, so small decays
+// cost no precision.
+constexpr int DCB = 16;
+__global__ void __launch_bounds__(128)
+delta_chunk_prefix_kernel(const float* __restrict__ P, const float* __restrict__ Q, float* __restrict__ start,
+                          float* __restrict__ state, size_t slot_stride, const int32_t* __restrict__ seq_chunk,
+                          const int32_t* __restrict__ seq_slot, int H, int dk, int dv) {
+    extern __shared__ float s_cur[];                    // [dk][DCB]: the state's rows of this block's columns
+    grid_dep_launch();
+    grid_dep_wait();
+    const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * DCB;
+    const int slot = seq_slot[s];
+    if (slot < 0) return;
+    const int n_cols = min(DCB, dv - col0);
+    float* mine = state + (size_t)slot * slot_stride + ((size_t)h * dv + col0) * dk;
+    for (int e = threadIdx.x; e < DCB * dk; e += blockDim.x) {
+        const int c = e / dk, i = e - c * dk;
+        s_cur[i * DCB + c] = c < n_cols ? mine[(size_t)c * dk + i] : 0.f;
+    }
+    for (int ch = seq_chunk[s]; ch < seq_chunk[s + 1]; ++ch) {
+        __syncthreads();
+        float* st = start + (((size_t)ch * H + h) * dv + col0) * dk;
+        for (int e = threadIdx.x; e < n_cols * dk; e += blockDim.x) {
+            const int c = e / dk, i = e - c * dk;
+            st[(size_t)c * dk + i] = s_cur[i * DCB + c];
+        }
+        const float* Pc = P + ((size_t)ch * H + h) * dk * dk;
+        const float* Qc = Q + (((size_t)ch * H + h) * dv + col0) * dk;
+        float acc[2][DCB];                              // rows threadIdx.x and threadIdx.x + 128 (dk is at most 256)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int i = threadIdx.x + r * 128;
+#pragma unroll
+            for (int c = 0; c < DCB; ++c) acc[r][c] = (i < dk && c < n_cols) ? Qc[(size_t)c * dk + i] : 0.f;
+        }
+        for (int j = 0; j < dk; ++j) {
+            const float p0 = threadIdx.x < dk ? Pc[(size_t)j * dk + threadIdx.x] : 0.f;
+            const float p1 = threadIdx.x + 128 < dk ? Pc[(size_t)j * dk + threadIdx.x + 128] : 0.f;
+            const float4* row = reinterpret_cast<const float4*>(s_cur + j * DCB);
+#pragma unroll
+            for (int c4 = 0; c4 < DCB / 4; ++c4) {
+                const float4 x = row[c4];
+                acc[0][4 * c4] = fmaf(p0, x.x, acc[0][4 * c4]);         acc[1][4 * c4] = fmaf(p1, x.x, acc[1][4 * c4]);
+                acc[0][4 * c4 + 1] = fmaf(p0, x.y, acc[0][4 * c4 + 1]); acc[1][4 * c4 + 1] = fmaf(p1, x.y, acc[1][4 * c4 + 1]);
+                acc[0][4 * c4 + 2] = fmaf(p0, x.z, acc[0][4 * c4 + 2]); acc[1][4 * c4 + 2] = fmaf(p1, x.z, acc[1][4 * c4 + 2]);
+                acc[0][4 * c4 + 3] = fmaf(p0, x.w, acc[0][4 * c4 + 3]); acc[1][4 * c4 + 3] = fmaf(p1, x.w, acc[1][4 * c4 + 3]);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int i = threadIdx.x + r * 128;
+            if (i < dk) {
+#pragma unroll
+                for (int c = 0; c < DCB; ++c) s_cur[i * DCB + c] = acc[r][c];
+            }
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_cols * dk; e += blockDim.x) {
+        const int c = e / dk, i = e - c * dk;
+        mine[(size_t)c * dk + i] = s_cur[i * DCB + c];
     }
 }
 
@@ -677,6 +747,20 @@ QS_API int qs_state_scan(int mode, float* o, long long ldo, const void* q, long 
     if ((rc = qs_check_launch("state_scan chunk prefix")) != QS_OK) return rc;
     return SCAN(3, chunk_state, per_chunk, chunk_start, chunk_ids, n_chunks);
 #undef SCAN
+}
+
+// See delta_chunk_prefix_kernel.  seq_chunk (n_seq + 1) names each sequence's chunks; a sequence's slot must be a row
+// of `state` (or negative: skipped).
+QS_API int qs_delta_chunk_prefix(const float* P, const float* Q, float* start, float* state, long long slot_stride,
+                                 const int32_t* seq_chunk, const int32_t* seq_slot, int n_seq, int H, int dk, int dv,
+                                 cudaStream_t stream) {
+    if (n_seq == 0) return QS_OK;
+    QS_REQUIRE(n_seq > 0 && H > 0 && dk > 0 && dk <= 256 && dv > 0 && H <= 65535, "delta_chunk_prefix: bad sizes");
+    const size_t smem = (size_t)dk * DCB * sizeof(float);
+    cudaError_t e = qs_launch_dependent(delta_chunk_prefix_kernel, dim3(n_seq, H, (dv + DCB - 1) / DCB), dim3(128), smem, stream,
+                                        P, Q, start, state, (size_t)slot_stride, seq_chunk, seq_slot, H, dk, dv);
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "delta_chunk_prefix: %s", cudaGetErrorString(e));
+    return qs_check_launch("delta_chunk_prefix");
 }
 
 QS_API int qs_token_shift(void* out, long long ldo, long long mix_stride, const void* h, long long ldh, int dtype,

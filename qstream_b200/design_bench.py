@@ -496,7 +496,10 @@ def kernel_table_sefuvik(torch, np, pk, width=2048, T=4096, batch=32, ctx=2048):
         ms = t.kernel(lambda: ops.state_scan("delta", qo, ko, vo, state, starts, slots, n_seq, H, d, d, key_decay=decay, token_weight=beta,
                                              qk_group=H // Gq), repeats=5)
         if tag == "prompt":                             # decay, S^T k, the write and the read-out: 4 multiply-adds per element and token
-            add(f"state scan delta prompt {T} (in order)", "state scan decay prompt", ms, flops=8.0 * T * H * d * d, bound="fp32")
+            add(f"state scan delta prompt {T} (in order: what short prompts take)", "", ms, flops=8.0 * T * H * d * d, bound="fp32")
+            ms = t.kernel(lambda: ops.state_scan("delta", qo, ko, vo, state, starts, slots, n_seq, H, d, d, key_decay=decay, token_weight=beta,
+                                                 qk_group=H // Gq, chunks=chunks), repeats=5)
+            add(f"state scan delta prompt {T} (chunks: three walks and a prefix)", "state scan decay prompt", ms, flops=8.0 * T * H * d * d, bound="fp32")
         else:
             add(f"state scan delta decode {batch}", "state scan decay decode", ms, 2 * state.numel() * 4)
     ql, kl, vl = (torch.randn(T, H * d, device=dev, dtype=bf) for _ in range(3))

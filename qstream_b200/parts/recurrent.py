@@ -191,7 +191,8 @@ class GatedDelta(Mixer):
     first matrices of the two bottlenecks are one product in the engine's type; the step sizes' projection and the
     decays' second matrix give 32-bit results.  One kernel runs the short convolutions (with the inputs that earlier
     steps left), silu, the unit norms, the decays and the step sizes, all in 32-bit; the scan walks each sequence in
-    order; the last kernel takes each head's unit RMS, the weight and the sigmoid gate."""
+    order (a long prompt: its chunks side by side, each as a linear map of the state it starts from, joined by a
+    prefix over the chunks); the last kernel takes each head's unit RMS, the weight and the sigmoid gate."""
     captures_any_step = True
 
     @classmethod
@@ -240,7 +241,7 @@ class GatedDelta(Mixer):
             ops.conv_state_update(held, q, k, v, nq, nv, s.conv_taps, b.seq_start, b.seq_slot, b.n_seq)
         o = ops.state_scan("delta", qo, ko, vo, step.state(cache_id, "matrix"), b.seq_start, b.seq_slot, b.n_seq,
                            s.n_heads, s.key_dim, s.value_dim, key_decay=decay, token_weight=beta,
-                           qk_group=s.n_heads // s.n_qk_heads)
+                           qk_group=s.n_heads // s.n_qk_heads, chunks=scan_chunks(b, h.device))
         y = ops.gated_group_norm(o, s.value_dim, self.norm, gate, "sigmoid", s.eps, h.dtype)
         return linear(y, self.w_out, None, residuals=residuals, out_dtype=out_dtype)
 

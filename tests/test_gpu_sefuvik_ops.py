@@ -277,3 +277,53 @@ def test_the_bfloat16_kernels_take_the_same_masks(mask, sizes):
                                 gate=gd[places].contiguous() if gd is not None else None, **opts)
     np.testing.assert_allclose(got.float().cpu().numpy(), want[places], rtol=0, atol=1e-4 if maps > 1 else 1e-2)
     assert int(pages.status.item()) == 0
+
+
+@pytest.mark.parametrize("sizes", [(4, 2, 8, 12), (2, 1, 64, 64), (3, 3, 10, 14), (2, 2, 128, 96)])
+def test_the_delta_rule_in_chunks_equals_the_walk_in_order(sizes):
+    """Two prompts of unequal lengths cut into chunks of 64 (the last ones ragged), from states that a first step
+    left, against the same kernel's walk in order; small decays among them (a chunk's product of decays underflows
+    nothing, since nothing is divided by it)."""
+    H, G, d, dv = sizes
+    rng = np.random.default_rng(H * d)
+    lens, first = (333, 200), 17
+    T = sum(lens)
+    unit = lambda x: x / np.sqrt((x * x).sum(-1, keepdims=True) + 1e-6)      # noqa: E731
+    q = dev(unit(rng.normal(size=(T, G, d))).reshape(T, G * d) * d ** -0.5)
+    k = dev(unit(rng.normal(size=(T, G, d))).reshape(T, G * d))
+    v = dev(rng.normal(size=(T, H * dv)))
+    decay = dev(np.where(rng.random((T, H * d)) < 0.1, rng.uniform(1e-3, 0.5, (T, H * d)), rng.uniform(0.9, 1.0, (T, H * d))))
+    beta = dev(rng.uniform(0.0, 1.0, (T, H)))
+    walk = dict(key_decay=decay, token_weight=beta, qk_group=H // G)
+    slots, n_slots = (2, 0), 3
+    starts = [0, lens[0], T]
+
+    def run(chunked):
+        state = torch.zeros((n_slots, H, dv, d), dtype=torch.float32, device=DEV)
+        outs = [None, None]
+        # a first step of 17 tokens each in order, then the rest in one step
+        rows1 = np.concatenate([np.arange(starts[i], starts[i] + first) for i in range(2)])
+        rows2 = np.concatenate([np.arange(starts[i] + first, starts[i + 1]) for i in range(2)])
+        for rows, n_each in ((rows1, [first, first]), (rows2, [n - first for n in lens])):
+            sel = torch.tensor(rows, device=DEV)
+            seq_start = np.concatenate([[0], np.cumsum(n_each)])
+            chunks = None
+            if chunked and max(n_each) > 64:
+                cs, owners, row = [0], [0], 0
+                for n in n_each:
+                    cs += [row + min(n, a + 64) for a in range(0, n, 64)]
+                    row += n
+                    owners.append(len(cs) - 1)
+                chunks = (i32(cs), i32(np.arange(len(cs) - 1)), i32(owners), len(cs) - 1)
+            o = ops.state_scan("delta", q[sel].contiguous(), k[sel].contiguous(), v[sel].contiguous(), state, i32(seq_start), i32(slots), 2,
+                               H, d, dv, chunks=chunks, key_decay=decay[sel].contiguous(), token_weight=beta[sel].contiguous(),
+                               qk_group=H // G)
+            outs[0 if rows is rows1 else 1] = o.cpu().numpy()
+        return outs, state.cpu().numpy()
+    (a1, a2), sa = run(False)
+    (b1, b2), sb = run(True)
+    np.testing.assert_array_equal(a1, b1)
+    scale = max(1.0, np.abs(a2).max())
+    np.testing.assert_allclose(b2, a2, rtol=0, atol=2e-5 * scale)
+    np.testing.assert_allclose(sb, sa, rtol=0, atol=2e-5 * max(1.0, np.abs(sa).max()))
+    assert np.abs(sa[1]).max() == 0.0 and np.abs(sb[1]).max() == 0.0
