@@ -98,7 +98,7 @@ class AttentionSpec:
     by sigmoid(W_g h) before the output projection.  `value_mix`: "first" keeps the layer's
     values for later layers of the same step, "blend" caches (1 - l) v + l v_first with its
     scalar tensor "value_mix" as l.
-    `chunk` c > 0: a query sees only the keys of its own chunk of c positions, counted from position 0 (no window then).
+    `chunk` c > 0: a query sees only the keys of its own chunk of c positions; chunks tile the sequence from its first token (no window then).
     `keep_first` n > 0 with a window: the sequence's first n keys stay visible to every later query.
     `sink`: a learned number per query head (tensor "sink") whose exponential joins the softmax's denominator without a
     key or a value.  `maps` = 2 (differential attention): q and k hold two maps per head side by side, each an attention

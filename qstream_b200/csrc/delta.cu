@@ -1,8 +1,9 @@
 // What a gated delta rule needs between its projections and its scan.
 //
 // q, k (G heads of dk) and v (H heads of dv) each pass a short causal convolution over time per channel
-// (taps [channels, n], the last column is the current token's; zeros before a sequence's start) and silu; q and k
-// then become unit vectors per head, x / sqrt(sum x^2 + unit_eps), q also times q_scale.  The decay per token, head
+// (taps [channels, n]: tap n - 1 weighs the token itself, tap n - 1 - j the token j places back, and what lies before a
+// sequence counts as zero) and silu; q and k then become unit vectors per head, x / sqrt(sum x^2 + unit_eps), q also
+// times q_scale.  The decay per token, head
 // and key channel is g = exp(-exp(A_log_h) * softplus(a)), the step size per token and head beta = sigmoid(b).
 // Everything is 32-bit and leaves in 32-bit: these values enter the recurrence.
 //

@@ -544,7 +544,7 @@ def delta_prepare(q, k, v, conv_q, conv_k, conv_v, conv_state, a, b, a_log, tok_
                   key_dim, value_dim, q_scale: float, unit_eps: float):
     """What a gated delta rule needs between its projections and its scan.  q, k [T, n_qk_heads * key_dim] and v
     [T, n_heads * value_dim] (views of one product's result) pass a causal convolution over time per channel (taps
-    [channels, n], the last column the current token's; the n - 1 inputs before a step's first token come from
+    [channels, n], tap n - 1 weighing the token itself; the n - 1 inputs before a step's first token come from
     `conv_state` [slots, n - 1, channels of q | k | v]) and silu; q and k become unit vectors per head
     (x / sqrt(sum x^2 + unit_eps)), q times q_scale.  a float32 [T, n_heads * key_dim] gives the decays
     exp(-exp(a_log_h) softplus(a)), b float32 [T, n_heads] the step sizes sigmoid(b).  Returns float32 q, k, v, decays,

@@ -73,12 +73,14 @@ def rotate_half(x, positions, dims, base):
 # ----------------------------------------------------------------------------- visibility
 
 def visible_window(i, j, size, keep_first):
-    """Sliding window with kept first tokens: j <= i and (i - j < size or j < keep_first); size 0: every j <= i."""
+    """Causal; of the keys behind it a query reaches the nearest `size` (itself among them) and, whatever their
+    distance, those at places below `keep_first`.  size 0: all keys behind it."""
     return j <= i and (not size or i - j < size or j < keep_first)
 
 
 def visible_chunk(i, j, size):
-    """Chunks counted from position 0: j <= i in the same chunk; size 0: every j <= i."""
+    """Causal, and only inside the query's own block of `size` places (blocks tile the sequence from its first token);
+    size 0: all keys behind it."""
     return j <= i and (not size or i // size == j // size)
 
 
@@ -124,8 +126,8 @@ def retention(m, w, p, h, eps):
 
 
 def short_conv(x, taps):
-    """Causal convolution over time per channel: x [T, C], taps [C, n] with the last column the current token's,
-    zeros before the start."""
+    """Causal convolution over time per channel: x [T, C], taps [C, n]; tap n - 1 weighs the token itself, tap n - 1 - j the token j
+    places back; what lies before the sequence counts as zero."""
     T, C = x.shape
     n = taps.shape[1]
     pad = np.concatenate([np.zeros((n - 1, C)), x])
@@ -183,7 +185,7 @@ def parallel_mixer(m, w, p, h, eps):
 
 def differential_attention(m, w, p, h, eps):
     """Two attention maps over the same values, o = a1 - lambda a2, unit RMS per head, times (1 - diff); sliding
-    window with kept first tokens; biases on q, k, v; no rotation."""
+    window that also reaches the sequence's first places; biases on q, k, v; positions do not enter."""
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = (h @ w[p + "q"].T + w[p + "q.b"]).reshape(T, H, 2, d)

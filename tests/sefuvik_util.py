@@ -72,9 +72,9 @@ CONFIG_B = {
 CONFIG_C = {
     "architecture": "Sefuvik", "vocab": 160, "width": 128, "norm": {"eps": 1e-6}, "streams": 4,
     "layers": [
-        attention_layer(4, 2, 32, 64, 64, 70, 32 ** -0.5, 0.3, mlp=dense(192)),
-        parallel_layer((4, 2, 64, 32, 128, 0.125, (32, 5e4)), (4, 4, 32, 32, 3), (0.8, 0.9), mlp=dense(128)),
-        retention_layer(32, 64, (0.96875, 0.9990234375), rot=(32, 1e6), mlp=dense(96)),
+        attention_layer(4, 2, 32, 64, 64, 70, 32 ** -0.5, 0.25, mlp=dense(192)),
+        parallel_layer((4, 2, 64, 32, 128, 0.11, (32, 2e4)), (4, 4, 32, 32, 3), (0.75, 0.85), mlp=dense(128)),
+        retention_layer(32, 64, (0.9375, 0.998046875), rot=(16, 3e5), mlp=dense(96)),
         parallel_layer((2, 2, 32, 32, 64, 0.2, (32, 1e4)), (2, 1, 64, 64, 4), (1.0, 0.5), mlp=None),
         attention_layer(2, 1, 64, 32, 128, 0, 0.125, 0.25, mlp=dense(64)),
     ],
