@@ -79,6 +79,18 @@ CONFIG_C = {
         attention_layer(2, 1, 64, 32, 128, 0, 0.125, 0.25, mlp=dense(64)),
     ],
 }
+# E: wider, for long requests: head sizes of 32 to 80 that the tensor-core kernels take, three query heads to a key head,
+#    a chunk and a window that are no multiples of a page and span several, kept first tokens, long enough prompts for
+#    the scans' chunks.
+CONFIG_E = {
+    "architecture": "Sefuvik", "vocab": 512, "width": 256, "norm": {"eps": 1e-6}, "streams": 3,
+    "layers": [
+        parallel_layer((6, 2, 32, 48, 100, 0.2, (16, 1e4)), (4, 2, 48, 32, 4), (0.6, 0.9), mlp=dense(320)),
+        attention_layer(6, 2, 32, 80, 150, 9, 0.15, 0.2, mlp=dense(192)),
+        retention_layer(48, 64, (0.98, 0.9995, 0.9), rot=(24, 1e5), mlp=dense(256)),
+        attention_layer(3, 3, 64, 64, 70, 0, 0.1, 0.35, mlp=None),
+    ],
+}
 # single mixers: one layer each, no feed-forward, one copy
 CONFIG_R = {"architecture": "Sefuvik", "vocab": 64, "width": 48, "norm": {"eps": 1e-5}, "streams": 2,
             "layers": [retention_layer(16, 8, (0.8, 0.995, 1.0), rot=(8, 1e3), mlp=None)]}
@@ -86,7 +98,7 @@ CONFIG_D = {"architecture": "Sefuvik", "vocab": 64, "width": 48, "norm": {"eps":
             "layers": [attention_layer(4, 2, 8, 16, 23, 3, 0.35, 0.3, mlp=None)]}
 CONFIG_P = {"architecture": "Sefuvik", "vocab": 64, "width": 48, "norm": {"eps": 1e-5}, "streams": 2,
             "layers": [parallel_layer((4, 1, 8, 8, 21, 0.35, (8, 1e3)), (4, 2, 8, 16, 3), (0.9, 1.1), mlp=None)]}
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "R": CONFIG_R, "D": CONFIG_D, "P": CONFIG_P}
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "R": CONFIG_R, "D": CONFIG_D, "P": CONFIG_P, "E": CONFIG_E}
 
 
 def make_weights(cfg: dict, seed: int, decay_rank: int = 5, gate_rank: int = 7, gain_all: float = 1.0) -> dict[str, np.ndarray]:
@@ -158,7 +170,7 @@ def write_folder(folder, cfg: dict, weights: dict, dtype: str):
 
 def make_folder(tmp_path, which: str, dtype: str, seed: int = 0):
     cfg = CONFIGS[which]
-    weights = make_weights(cfg, seed + "ABCRDP".index(which), gain_all=1.0 if dtype == "float32" else 0.4)
+    weights = make_weights(cfg, seed + "ABCRDPE".index(which), gain_all=1.0 if dtype == "float32" else 0.4)
     return write_folder(tmp_path / f"sefuvik_{which}_{dtype}", cfg, weights, dtype), cfg
 
 

@@ -311,3 +311,44 @@ def test_a_model_made_from_a_seed_runs_and_saves(tmp_path):
         engine = qs.Engine(model, max_tokens=128, max_batch=1)
         slot = engine.acquire()
         assert_close(engine.step([slot], [toks], [all_places(50)]).cpu().numpy(), ref, "float32", "seeded model")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_wider_model_with_long_requests(models, dtype):
+    """Sizes that the tensor-core kernels take, requests of up to 900 tokens: a whole prompt; a prompt and 260 tokens
+    one by one (the window and the chunk pass over decoded tokens, pages fall out and kept ones stay); three unequal
+    requests in one batch, decoded together until each ends."""
+    key, pcfg, w, model = models("E", dtype)
+    rng = np.random.default_rng(21)
+    reqs = [random_tokens(rng, n, pcfg["vocab"]) for n in (900, 300, 70)]
+    refs = [reference(key, pcfg, w, t) for t in reqs]
+    engine = qs.Engine(model, max_tokens=64 * 24, max_batch=3)
+    slot = engine.acquire()
+    got = engine.step([slot], [reqs[0]], [all_places(900)]).cpu().numpy()
+    engine.release(slot)
+    assert_close(got, refs[0], dtype, "whole")
+    slot = engine.acquire()
+    got = [engine.step([slot], [reqs[0][:640]], [all_places(640)]).cpu().numpy()]
+    got += [engine.step([slot], [[t]], [[0]]).cpu().numpy() for t in reqs[0][640:]]
+    engine.release(slot)
+    assert_close(np.concatenate(got), refs[0], dtype, "a prompt, then one by one")
+    prompt = (830, 290, 1)
+    slots = [engine.acquire() for _ in reqs]
+    first = engine.step(slots, [t[:p] for t, p in zip(reqs, prompt)], [[p - 1] for p in prompt]).cpu().numpy()
+    rows = [[first[i]] for i in range(3)]
+    pos, live = list(prompt), [0, 1, 2]
+    while live:
+        for i in [i for i in live if pos[i] == len(reqs[i])]:
+            engine.release(slots[i])
+            live.remove(i)
+        if not live:
+            break
+        out = engine.step([slots[i] for i in live], [[reqs[i][pos[i]]] for i in live], [[0]] * len(live)).cpu().numpy()
+        for j, i in enumerate(live):
+            rows[i].append(out[j])
+            pos[i] += 1
+    for i in range(3):
+        assert_close(np.stack(rows[i]), refs[i][prompt[i] - 1:], dtype, f"request {i} in a batch")
+    engine.check_status()
+    engine.cache.check()
+    assert engine.cache.slots.n_free == engine.cache.slots.n_slots
