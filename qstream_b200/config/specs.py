@@ -57,11 +57,13 @@ class RotaryHalfSpec:
     frequencies in the YaRN manner: with dim(t) = rotary_dim ln(original / (2 pi t)) / (2 ln base),
     lo = max(floor(dim(fast)), 0), hi = min(ceil(dim(slow)), rotary_dim - 1) and
     ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), f_i becomes f_i / factor * ramp_i + f_i (1 - ramp_i), and cos
-    and sin are multiplied by 0.1 ln(factor) + 1."""
+    and sin are multiplied by 0.1 ln(factor) + 1.  `layout` "interleaved" pairs element 2i with 2i + 1 instead (same
+    angles); the kernels that rotate are told which."""
     rotary_dim: int
     base: float
     scaling: Optional[Mapping[str, float]] = None
     kind: str = "rotary_half"
+    layout: str = "half"
 
 
 @dataclass(frozen=True)
@@ -105,6 +107,11 @@ class AttentionSpec:
     of its own over the same values; with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + `diff` (four vectors of head_dim),
     o = a1 - lambda a2 per head, divided by its root mean square over the head's values (`eps` inside the root), times
     (1 - diff).
+    `qk_norm` "whole": q = W_q h and k = W_k h each pass one RMS norm over the whole projection (all heads at once,
+    plain weights "q_norm" and "k_norm" of that size, `eps` inside the root) before they are split into heads and rotated.
+    `values_from_keys`: there is no W_v; a key head's values are its keys as projected, before norm and rotation.
+    `fixed_sink`: a number whose exponential joins every softmax's denominator without a key or a value (0.0: one
+    more term of exp(0) = 1), with no tensor behind it.
     """
     width: int
     n_heads: int
@@ -128,6 +135,9 @@ class AttentionSpec:
     maps: int = 1
     diff: float = 0.0
     eps: float = 0.0
+    qk_norm: Optional[str] = None
+    values_from_keys: bool = False
+    fixed_sink: Optional[float] = None
 
     @property
     def scale(self) -> float:
@@ -146,7 +156,9 @@ class LatentAttentionSpec:
     W_dkv h gives the latent c (rank `kv_rank`, RMS-normed) and one rotated key part of `rot_dim` shared by all heads;
     only these are cached.  Per head the unrotated key is W_uk c and the value W_uv c (`v_head_dim`).  The score is
     (q_unrotated . k_unrotated + q_rotated . k_rotated) * `score_scale`.  `shares_cache`: the layer has no W_dkv and
-    reads the latents another layer cached, with its own W_uk, W_uv and queries."""
+    reads the latents another layer cached, with its own W_uk, W_uv and queries.  `sink`: a learned number per head
+    (tensor "sink") whose exponential joins the softmax's denominator, unscaled, without key or value.  `head_gate`:
+    head h's output is multiplied by sigmoid(W_g h)_h, W_g ("g") having one row per head."""
     width: int
     n_heads: int
     head_dim: int
@@ -160,6 +172,8 @@ class LatentAttentionSpec:
     shares_cache: bool = False
     kind: str = "latent_attention"
     names: Mapping[str, str] = field(default_factory=dict)
+    sink: bool = False
+    head_gate: bool = False
 
 
 @dataclass(frozen=True)
@@ -202,6 +216,24 @@ class DecayAttentionSpec:
     norm_per_head: bool = False
     norm_weight: bool = True
     gate_activation: str = "sigmoid"
+
+
+@dataclass(frozen=True)
+class GlaSpec:
+    """Gated linear attention: q = W_q h key_dim^-1/2, k = W_k h, v = W_v h per head; a decay per token, head and key
+    channel w = sigmoid(W_a2 (W_a1 h) + b)^(1 / `tau`) from a two-matrix bottleneck (`decay_rank`, -1: whatever the
+    checkpoint holds); S_t = diag(w_t) S_{t-1} + k_t v_t^T, o_t = S_t^T q_t.  Each head's o gets an RMS norm over
+    value_dim with a weight of that size shared by the heads; the concatenated heads are multiplied by silu(W_g h) and
+    projected by W_o.  State per sequence: S [heads, value_dim, key_dim] in 32-bit; the decays and the walk are 32-bit."""
+    width: int
+    n_heads: int
+    key_dim: int
+    value_dim: int
+    tau: float
+    eps: float
+    decay_rank: int = -1
+    kind: str = "gla"
+    names: Mapping[str, str] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
@@ -316,7 +348,12 @@ class RoutedExpertsSpec:
     groups of neighbours, a group's score is the sum of its two largest choice scores, and only experts of the best
     `keep` groups can be chosen; the `top` largest choice scores win; their weights are s * `route_scale`, not
     renormalised.  `shared_inner` > 0: one more expert of that size runs for every token and is added, multiplied by
-    sigmoid(w_sg . h)."""
+    sigmoid(w_sg . h).
+    Options: `scores` "softmax": s = softmax(z) over all experts; `group_score` "max": a group's score is its largest
+    choice score; `correction` False: no correction tensor; `shared_gate` False: the shared expert is added as it is.
+    `gated`: every expert (the shared one too) is W_down y with g = min(W_gate h, limit), u = clamp(W_up h, -limit,
+    limit), y = g sigmoid(`glu_alpha` g) (u + `glu_shift`) (tensors "gate<e>", "shared_gate_proj"); `limit` for the
+    routed experts, `shared_limit` for the shared one (0: no clamp)."""
     width: int
     n_experts: int
     inner: int
@@ -328,6 +365,15 @@ class RoutedExpertsSpec:
     shared_inner: int = 0
     kind: str = "routed_experts"
     names: Mapping[str, str] = field(default_factory=dict)
+    scores: str = "sigmoid"
+    group_score: str = "top2"
+    correction: bool = True
+    shared_gate: bool = True
+    gated: bool = False
+    limit: float = 0.0
+    shared_limit: float = 0.0
+    glu_alpha: float = 1.702
+    glu_shift: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -343,6 +389,8 @@ class BlockSpec:
     arrangement "sandwich": a norm before and after each sublayer, x in 32-bit:
         x += norm_1b(mixer(norm_1(x))); x += norm_2b(ffn(norm_2(x)))
                                         (norms: "input", "post_input", and with a feed-forward "post_mixer", "post_ffn")
+    arrangement "post_norm": the sublayers read the 32-bit stream itself and a norm meets their results only:
+        x += norm_1(mixer(x)); x += norm_2(ffn(x))      (norms: "post_input", and with a feed-forward "post_ffn")
     arrangement "hyper": the stream in several copies, in 32-bit; each sublayer reads and writes it as its
         `HyperConnectionSpec` says (`connections`: "mixer", and with a feed-forward "ffn"); norms "input", "post_mixer".
     """

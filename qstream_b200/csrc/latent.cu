@@ -13,7 +13,8 @@
 //
 // The rotation pairs element i with i + dims/2 ("rotate half"): (u, v) -> (u cos a - v sin a, v cos a + u sin a)
 // times `mag`, a = position * freq[i], with the frequencies given by the caller (any scaling of them is the
-// caller's business).  Angles are taken in double precision, everything else in 32-bit, rounded once.
+// caller's business); with `interleaved` the pairs are elements 2i and 2i + 1 instead.  Angles are taken in double
+// precision, everything else in 32-bit, rounded once.
 #include "common.cuh"
 
 namespace {
@@ -25,7 +26,8 @@ __global__ void latent_prepare_kernel(T* __restrict__ cq_out, size_t ldcq, const
                                       int kv_rank, int rot_dim, int rot_dims, const double* __restrict__ freq, float mag,
                                       float eps, const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
                                       const int32_t* __restrict__ page_table, int max_pages, int page_shift,
-                                      T* __restrict__ k_cache, T* __restrict__ v_cache, int32_t* __restrict__ status) {
+                                      T* __restrict__ k_cache, T* __restrict__ v_cache, int32_t* __restrict__ status,
+                                      int interleaved) {
     __shared__ float scratch[33];
     grid_dep_launch();
     grid_dep_wait();
@@ -58,12 +60,13 @@ __global__ void latent_prepare_kernel(T* __restrict__ cq_out, size_t ldcq, const
     const int half = rot_dims >> 1;
     for (int i = threadIdx.x; i < rot_dim; i += blockDim.x) {
         if (i >= rot_dims) { kdst[kv_rank + i] = kr[i]; continue; }
-        const int j = i < half ? i : i - half;
+        const int j = interleaved ? i >> 1 : (i < half ? i : i - half);
+        const bool first = interleaved ? !(i & 1) : i < half;
         double sn, cs;
         sincos((double)pos * freq[j], &sn, &cs);
         const float c = (float)cs * mag, sv = (float)sn * mag;
-        const float u = to_f32(kr[j]), v = to_f32(kr[j + half]);
-        kdst[kv_rank + i] = from_f32<T>(i < half ? u * c - v * sv : v * c + u * sv);
+        const float u = to_f32(kr[interleaved ? 2 * j : j]), v = to_f32(kr[interleaved ? 2 * j + 1 : j + half]);
+        kdst[kv_rank + i] = from_f32<T>(first ? u * c - v * sv : v * c + u * sv);
     }
 }
 
@@ -72,7 +75,8 @@ __global__ void latent_prepare_kernel(T* __restrict__ cq_out, size_t ldcq, const
 template <typename T>
 __global__ void latent_q_rotate_kernel(T* __restrict__ q_abs, size_t ldqa, const T* __restrict__ q, size_t ldq, int H,
                                        int dn, int dr, int r, int rot_dims, const double* __restrict__ freq, float mag,
-                                       const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos) {
+                                       const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
+                                       int interleaved) {
     extern __shared__ float cs_sn[];                    // the token's cosines and sines, taken once for all heads
     grid_dep_launch();
     grid_dep_wait();
@@ -93,10 +97,11 @@ __global__ void latent_q_rotate_kernel(T* __restrict__ q_abs, size_t ldqa, const
         T* dst = q_abs + t * ldqa + (size_t)h * (r + dr) + r;
         if (slot < 0) { dst[i] = from_f32<T>(0.f); continue; }
         if (i >= rot_dims) { dst[i] = src[i]; continue; }
-        const int j = i < half ? i : i - half;
+        const int j = interleaved ? i >> 1 : (i < half ? i : i - half);
+        const bool first = interleaved ? !(i & 1) : i < half;
         const float c = cs_sn[2 * j], sv = cs_sn[2 * j + 1];
-        const float u = to_f32(src[j]), v = to_f32(src[j + half]);
-        dst[i] = from_f32<T>(i < half ? u * c - v * sv : v * c + u * sv);
+        const float u = to_f32(src[interleaved ? 2 * j : j]), v = to_f32(src[interleaved ? 2 * j + 1 : j + half]);
+        dst[i] = from_f32<T>(first ? u * c - v * sv : v * c + u * sv);
     }
 }
 
@@ -149,7 +154,7 @@ QS_API int qs_latent_prepare(void* cq_out, long long ldcq, const void* dq, long 
                              int rot_dim, int rot_dims, const double* freq, float mag, float eps, int dtype,
                              const int32_t* tok_slot, const int32_t* tok_pos, const int32_t* page_table, int max_pages,
                              int page_tokens, void* k_cache, void* v_cache, int T_tokens, int32_t* status,
-                             cudaStream_t stream) {
+                             int interleaved, cudaStream_t stream) {
     if (T_tokens == 0) return QS_OK;
     QS_REQUIRE(T_tokens > 0 && (dq || dkv), "latent_prepare: nothing to do");
     QS_REQUIRE(!dq || (cq_out && wq && q_rank > 0), "latent_prepare: a query latent without its norm");
@@ -164,7 +169,7 @@ QS_API int qs_latent_prepare(void* cq_out, long long ldcq, const void* dq, long 
     cudaError_t e;
 #define GO(T) e = qs_launch_dependent(latent_prepare_kernel<T>, dim3(T_tokens), dim3(threads), 0, stream, (T*)cq_out, (size_t)ldcq, \
         (const T*)dq, (size_t)lddq, wq, wq_dtype, q_rank, (const T*)dkv, (size_t)lddkv, wkv, wkv_dtype, kv_rank, rot_dim, rot_dims, \
-        freq, mag, eps, tok_slot, tok_pos, page_table, max_pages, shift, (T*)k_cache, (T*)v_cache, status)
+        freq, mag, eps, tok_slot, tok_pos, page_table, max_pages, shift, (T*)k_cache, (T*)v_cache, status, interleaved)
     if (dtype == QS_F32) GO(float);
     else if (dtype == QS_BF16) GO(__nv_bfloat16);
     else return qs_fail(QS_ERR_INVALID_INPUT, "latent_prepare: unknown dtype %d", dtype);
@@ -175,14 +180,14 @@ QS_API int qs_latent_prepare(void* cq_out, long long ldcq, const void* dq, long 
 
 QS_API int qs_latent_q_rotate(void* q_abs, long long ldqa, const void* q, long long ldq, int dtype, int H, int dn, int dr,
                               int r, int rot_dims, const double* freq, float mag, const int32_t* tok_slot,
-                              const int32_t* tok_pos, int T_tokens, cudaStream_t stream) {
+                              const int32_t* tok_pos, int T_tokens, int interleaved, cudaStream_t stream) {
     if (T_tokens == 0 || dr == 0) return QS_OK;
     QS_REQUIRE(T_tokens > 0 && H > 0 && dn >= 0 && dr > 0 && r > 0 && freq, "latent_q_rotate: bad sizes");
     QS_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dr, "latent_q_rotate: %d rotated of %d dims", rot_dims, dr);
     const int threads = H * dr >= 1024 ? 256 : 128;
     cudaError_t e;
 #define GO(T) e = qs_launch_dependent(latent_q_rotate_kernel<T>, dim3(T_tokens), dim3(threads), (size_t)(rot_dims > 0 ? rot_dims : 1) * sizeof(float), stream, (T*)q_abs, (size_t)ldqa, \
-        (const T*)q, (size_t)ldq, H, dn, dr, r, rot_dims, freq, mag, tok_slot, tok_pos)
+        (const T*)q, (size_t)ldq, H, dn, dr, r, rot_dims, freq, mag, tok_slot, tok_pos, interleaved)
     if (dtype == QS_F32) GO(float);
     else if (dtype == QS_BF16) GO(__nv_bfloat16);
     else return qs_fail(QS_ERR_INVALID_INPUT, "latent_q_rotate: unknown dtype %d", dtype);

@@ -4,7 +4,8 @@
 //                 neighbours, a group's score the sum of its two largest choice scores, only the best `keep` groups
 //                 stay (the others count as minus infinity); the `top` largest choice scores win (equal scores: the
 //                 lower index); weights s * scale of the winners, not renormalised; optionally sigmoid of one more
-//                 logit per token (the gate of a shared expert)
+//                 logit per token (the gate of a shared expert).  `score_kind` 1: s = softmax(z) over all experts
+//                 instead of the sigmoid; `group_kind` 1: a group's score is its largest choice score
 //   few tokens    moe_expert_up / moe_expert_down: every (token, chosen expert) pair reads its expert's matrices
 //                 through the routing table on the device, so a step can be captured and replayed
 //   many tokens   moe_sort orders the pairs by expert; the caller runs one matrix product per expert over its rows
@@ -20,7 +21,8 @@ constexpr int MAX_EXPERTS = 1024;
 // One warp per token.  Lanes compute the scores; lane 0 selects.
 __global__ void moe_route_kernel(int32_t* __restrict__ idx, float* __restrict__ wts, float* __restrict__ shared_gate,
                                  const float* __restrict__ z, size_t ldz, const void* __restrict__ corr, int corr_dtype,
-                                 int T, int E, int top, int groups, int keep, float scale, int gate_col) {
+                                 int T, int E, int top, int groups, int keep, float scale, int gate_col, int score_kind,
+                                 int group_kind) {
     extern __shared__ float sm[];                       // per warp: s [E], choice [E], group score [groups]
     grid_dep_launch();
     grid_dep_wait();
@@ -31,8 +33,16 @@ __global__ void moe_route_kernel(int32_t* __restrict__ idx, float* __restrict__ 
     float* choice = s + E;
     float* gscore = choice + E;
     const float* zr = z + (size_t)t * ldz;
+    float z_max = -INFINITY, inv_sum = 1.0f;
+    if (score_kind == 1) {                              // softmax over all experts: the largest logit, then the sum
+        for (int e = lane; e < E; e += 32) z_max = fmaxf(z_max, zr[e]);
+        for (int off = 16; off > 0; off >>= 1) z_max = fmaxf(z_max, __shfl_xor_sync(0xffffffffu, z_max, off));
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) sum += expf(zr[e] - z_max);
+        inv_sum = 1.0f / warp_sum(sum);
+    }
     for (int e = lane; e < E; e += 32) {
-        s[e] = sigmoid_f32(zr[e]);
+        s[e] = score_kind == 1 ? expf(zr[e] - z_max) * inv_sum : sigmoid_f32(zr[e]);
         choice[e] = s[e] + (corr ? load_as_f32(corr, corr_dtype, e) : 0.f);
     }
     if (shared_gate && lane == 0 && gate_col >= 0) shared_gate[t] = sigmoid_f32(zr[gate_col]);
@@ -45,7 +55,7 @@ __global__ void moe_route_kernel(int32_t* __restrict__ idx, float* __restrict__ 
                 const float c = choice[e];
                 if (c > a) { b = a; a = c; } else if (c > b) b = c;
             }
-            gscore[g] = per > 1 ? a + b : a;
+            gscore[g] = (per > 1 && group_kind == 0) ? a + b : a;
         }
         __syncwarp();
         if (lane == 0) {
@@ -205,7 +215,7 @@ __global__ void moe_combine_kernel(float* __restrict__ out, size_t ldo, const TY
 
 QS_API int qs_moe_route(int32_t* idx, float* wts, float* shared_gate, const float* z, long long ldz, const void* corr,
                         int corr_dtype, int T, int E, int top, int groups, int keep, float scale, int gate_col,
-                        cudaStream_t stream) {
+                        int score_kind, int group_kind, cudaStream_t stream) {
     if (T == 0) return QS_OK;
     QS_REQUIRE(T > 0 && E > 0 && E <= MAX_EXPERTS && top > 0 && top <= E, "moe_route: bad sizes T=%d E=%d top=%d", T, E, top);
     QS_REQUIRE(groups > 0 && E % groups == 0 && keep > 0 && keep <= groups, "moe_route: %d experts in %d groups, %d kept", E, groups, keep);
@@ -213,7 +223,8 @@ QS_API int qs_moe_route(int32_t* idx, float* wts, float* shared_gate, const floa
     const int warps = 4;
     const size_t smem = (size_t)warps * (2 * E + groups) * sizeof(float);
     cudaError_t e = qs_launch_dependent(moe_route_kernel, dim3((T + warps - 1) / warps), dim3(warps * 32), smem, stream, idx, wts,
-                                        shared_gate, z, (size_t)ldz, corr, corr_dtype, T, E, top, groups, keep, scale, gate_col);
+                                        shared_gate, z, (size_t)ldz, corr, corr_dtype, T, E, top, groups, keep, scale, gate_col, score_kind,
+                                        group_kind);
     if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "moe_route: %s", cudaGetErrorString(e));
     return qs_check_launch("moe_route");
 }

@@ -52,7 +52,8 @@ _SIGNATURES = {
     "qs_residual_rmsnorm": ([c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int,
                              c_longlong, c_float, c_void_p, c_int, c_float, c_int, c_int, c_float, c_void_p], c_int),
     "qs_gated_group_norm": ([c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p, c_int, c_void_p, c_int,
-                             c_longlong, c_int, c_int, c_int, c_int, c_float, c_void_p], c_int),
+                             c_longlong, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p], c_int),
+    "qs_clamped_glu": ([c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p], c_int),
     "qs_activate": ([c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p], c_int),
     "qs_gated_act": ([c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p], c_int),
     "qs_embedding_hashed": ([c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_longlong, c_longlong, c_longlong,
@@ -61,7 +62,7 @@ _SIGNATURES = {
     "qs_state_scan": ([c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int,
                        c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
                        c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                       c_void_p, c_void_p, c_longlong, c_float, c_int, c_void_p], c_int),
+                       c_void_p, c_void_p, c_longlong, c_float, c_int, c_float, c_void_p], c_int),
     "qs_delta_chunk_prefix": ([c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                c_void_p], c_int),
     "qs_mlstm_gates": ([c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_float, c_void_p, c_longlong,
@@ -72,13 +73,13 @@ _SIGNATURES = {
                         c_int, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p], c_int),
     "qs_latent_prepare": ([c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p, c_longlong,
                            c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_float, c_int, c_void_p, c_void_p,
-                           c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p], c_int),
+                           c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p], c_int),
     "qs_latent_q_rotate": ([c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int,
-                            c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p], c_int),
+                            c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p], c_int),
     "qs_head_linear": ([c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_int, c_int,
                         c_int, c_int, c_void_p], c_int),
     "qs_moe_route": ([c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                      c_int, c_float, c_int, c_void_p], c_int),
+                      c_int, c_float, c_int, c_int, c_int, c_void_p], c_int),
     "qs_moe_expert_up": ([c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                           c_int, c_int, c_int, c_void_p], c_int),
     "qs_moe_expert_down": ([c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
@@ -411,21 +412,22 @@ def rmsnorm(x, weight, eps: float, offset: float = 0.0, out_dtype=None, update=N
     return h
 
 
-def gated_group_norm(o, group: int, weight, gate, gate_activation, eps: float, out_dtype) -> torch.Tensor:
+def gated_group_norm(o, group: int, weight, gate, gate_activation, eps: float, out_dtype, gate_span: int = 1) -> torch.Tensor:
     """out = o / sqrt(mean over each group of `group` consecutive elements of o^2 + eps) * weight * act(gate);
-    group 0: no norm; weight and gate may be None.  Sums in 32-bit."""
+    group 0: no norm; weight and gate may be None.  `gate_span` n > 1: the gate has one column for every n
+    neighbouring columns of o (a value per head, say).  Sums in 32-bit."""
     rows, n, ldi = _rows(o)
     out = torch.empty((rows, n), dtype=out_dtype, device=o.device)
     ldg = 0
     if gate is not None:
         r2, n2, ldg = _rows(gate)
-        if (r2, n2) != (rows, n):
+        if (r2, n2 * int(gate_span)) != (rows, n):
             raise QStreamError(QsError.INVALID_INPUT, "gated_group_norm: the gate differs from o in shape")
     if weight is not None and weight.numel() != n:
         raise QStreamError(QsError.INVALID_INPUT, f"gated_group_norm: width {n} but weight {tuple(weight.shape)}")
     check(library().qs_gated_group_norm(ptr(out), dtype_code(out), n, ptr(o), dtype_code(o), ldi, ptr(weight),
                                         _code(weight), ptr(gate), _code(gate), ldg, ACTIVATIONS[gate_activation],
-                                        rows, n, int(group), float(eps), stream()))
+                                        rows, n, int(group), float(eps), int(gate_span), stream()))
     return out
 
 
@@ -442,6 +444,17 @@ def gated_act(ab: torch.Tensor, activation) -> torch.Tensor:
     F = two_f // 2
     out = torch.empty((rows, F), dtype=ab.dtype, device=ab.device)
     check(library().qs_gated_act(ptr(out), F, ptr(ab), ldi, dtype_code(ab), rows, F, ACTIVATIONS[activation], stream()))
+    return out
+
+
+def clamped_glu(ab: torch.Tensor, limit: float, alpha: float = 1.702, shift: float = 1.0) -> torch.Tensor:
+    """For ab = [a | b] ([rows, 2 F]): g = min(a, limit), u = clamp(b, -limit, limit), out = g sigmoid(alpha g) (u + shift),
+    in 32-bit, rounded once; limit <= 0: no clamp."""
+    rows, two_f, ldi = _rows(ab)
+    F = two_f // 2
+    out = torch.empty((rows, F), dtype=ab.dtype, device=ab.device)
+    check(library().qs_clamped_glu(ptr(out), F, ptr(ab), ldi, dtype_code(ab), rows, F, float(limit), float(alpha),
+                                   float(shift), stream()))
     return out
 
 
@@ -473,7 +486,8 @@ def keep_last_rows(dst: torch.Tensor, src: torch.Tensor, seq_start, seq_slot, n_
 
 def state_scan(mode: str, q, k, v, state, seq_start, seq_slot, n_seq, n_heads, key_dim, value_dim, head_decay=None,
                decay_logits=None, bonus=None, in_activation=None, chunks=None, token_decay=None, token_weight=None,
-               q_scale: float = 1.0, key_decay=None, qk_group: int = 1, want_output: bool = True) -> torch.Tensor:
+               q_scale: float = 1.0, key_decay=None, qk_group: int = 1, want_output: bool = True,
+               decay_power: float = 0.0) -> torch.Tensor:
     """Walk each sequence's tokens of this step through a per-head matrix state (float32 [slots, heads, value_dim,
     key_dim], updated in place); returns o [T, heads * value_dim] in float32.
     mode "decay": S <- decay_h S + k v^T, o = S^T q.  mode "wkv": o = (S + diag(bonus) k v^T)^T q, then
@@ -485,6 +499,8 @@ def state_scan(mode: str, q, k, v, state, seq_start, seq_slot, n_seq, n_heads, k
     reading number h // qk_group.  With `chunks` the delta rule runs the same walk three times over the chunks side by
     side (what a chunk does to an identity, what it writes from an empty state, and, once a prefix over the chunks has
     given each its starting state, the chunk's outputs).  In mode "decay" `q_scale` multiplies q as well.
+    mode "gla": S <- diag(w_t) S + k v^T, o = S^T (q q_scale), w_t = sigmoid(decay_logits)^`decay_power` per token and key
+    channel (float32 [T, heads * key_dim]), taken in 32-bit inside the walk.
     `chunks` = (chunk_start, chunk_ids, seq_chunk, n_chunks), int32 device tensors: every sequence of the step cut
     into consecutive chunks (rows chunk_start[c] .. chunk_start[c + 1] of the packed batch; sequence s owns chunks
     seq_chunk[s] .. seq_chunk[s + 1]; chunk_ids = 0 .. n_chunks - 1).  The chunks then run side by side and a
@@ -504,6 +520,8 @@ def state_scan(mode: str, q, k, v, state, seq_start, seq_slot, n_seq, n_heads, k
         chunk_state = torch.empty((n_chunks, n_heads * value_dim * key_dim), dtype=torch.float32, device=q.device)
         chunk_decay = torch.empty((n_chunks, n_heads * key_dim), dtype=torch.float32, device=q.device)
     per_token = token_decay if token_decay is not None else token_weight
+    if mode == "gla" and (decay_logits is None or decay_logits.dtype != torch.float32 or not decay_power > 0):
+        raise QStreamError(QsError.INVALID_INPUT, "state_scan: gated linear attention takes float32 decay logits and a positive power")
     if mode == "delta":
         decay_logits = key_decay
         if key_decay.dtype != torch.float32 or token_weight.dtype != torch.float32:
@@ -511,14 +529,14 @@ def state_scan(mode: str, q, k, v, state, seq_start, seq_slot, n_seq, n_heads, k
     if mode == "gated" and (token_decay.dtype != torch.float32 or token_decay.stride() != token_weight.stride()):
         raise QStreamError(QsError.INVALID_INPUT, "state_scan: the tokens' decays and weights must be float32 of one layout")
     check(library().qs_state_scan(
-        {"decay": 0, "wkv": 1, "gated": 2, "delta": 3}[mode], ptr(o), o.stride(0) if o is not None else 0, ptr(q), q.stride(0),
+        {"decay": 0, "wkv": 1, "gated": 2, "delta": 3, "gla": 4}[mode], ptr(o), o.stride(0) if o is not None else 0, ptr(q), q.stride(0),
         ptr(k), k.stride(0), ptr(v), v.stride(0) if v is not None else 0,
         dtype_code(q), ptr(decay_logits), decay_logits.stride(0) if decay_logits is not None else 0, ptr(head_decay),
         ptr(bonus), _code(bonus), ptr(state), state.stride(0), _int32(seq_start, "seq_start"),
         _int32(seq_slot, "seq_slot"), int(n_seq), T, n_heads, key_dim, value_dim, ACTIVATIONS[in_activation],
         ptr(chunk_start), ptr(chunk_ids), int(n_chunks), ptr(seq_chunk), ptr(chunk_state), ptr(chunk_decay),
         ptr(token_decay), ptr(token_weight), per_token.stride(0) if per_token is not None else 0, float(q_scale),
-        int(qk_group), stream()))
+        int(qk_group), float(decay_power), stream()))
     return o
 
 
@@ -610,12 +628,13 @@ def mlstm_output(o, m, weight, gate, n_heads: int, value_dim: int, eps: float, o
 def branch_norm(x, weight, eps: float, center: bool, out_dtype=None, branch=None, branch_weight=None, want_norm=True,
                 in_place=False):
     """With `branch`: x <- x + norm(branch) * branch_weight (in place; without a weight the plain sum).  With
-    `want_norm`: returns h = norm(x) * weight in `out_dtype` (`in_place`: written over x).  norm is the layer norm
-    without bias (`center`) or the RMS norm, statistics in 32-bit, eps inside the root."""
+    `want_norm`: returns h = norm(x) * weight in `out_dtype` (`in_place`: written over x); without a weight h is the
+    new x itself in `out_dtype`.  norm is the layer norm without bias (`center`) or the RMS norm, statistics in 32-bit,
+    eps inside the root."""
     rows, D, ldx = _rows(x)
     h = None
     if want_norm:
-        if weight is None or weight.numel() != D:
+        if weight is not None and weight.numel() != D:
             raise QStreamError(QsError.INVALID_INPUT, f"norm: width {D} but weight {None if weight is None else tuple(weight.shape)}")
         h = x if in_place else torch.empty((rows, D), dtype=out_dtype or x.dtype, device=x.device)
     ldy = 0
@@ -631,9 +650,10 @@ def branch_norm(x, weight, eps: float, center: bool, out_dtype=None, branch=None
 
 
 def latent_prepare(dq, q_norm, q_rank, dkv, kv_norm, kv_rank, rot_dim, rot_dims, freq, mag, eps, tok_slot, tok_pos,
-                   page_table, page_tokens, k_cache, v_cache, status):
+                   page_table, page_tokens, k_cache, v_cache, status, interleaved=False):
     """RMS norm of the query latent dq [T, q_rank] -> returned; RMS norm of the key latent dkv[:, :kv_rank] and the
-    rotation (rotate-half pairs, `freq` float64 [rot_dims / 2], cos and sin times `mag`) of dkv[:, kv_rank:], written
+    rotation (pairs (i, i + rot_dims / 2), or (2i, 2i + 1) if `interleaved`; `freq` float64 [rot_dims / 2], cos and sin
+    times `mag`) of dkv[:, kv_rank:], written
     into the cache entry as keys [c | rotated part] and values c.  dkv None: a layer that reads another's cache."""
     ref = dq if dq is not None else dkv
     T = ref.shape[0]
@@ -645,16 +665,17 @@ def latent_prepare(dq, q_norm, q_rank, dkv, kv_norm, kv_rank, rot_dim, rot_dims,
         _int32(tok_slot, "tok_slot"), _int32(tok_pos, "tok_pos"),
         _int32(page_table, "page_table") if dkv is not None else None, page_table.shape[1] if dkv is not None else 0,
         int(page_tokens), ptr(k_cache) if dkv is not None else None, ptr(v_cache) if dkv is not None else None, T,
-        ptr(status), stream()))
+        ptr(status), int(bool(interleaved)), stream()))
     return cq
 
 
-def latent_q_rotate(q_abs, q, n_heads, dim, rot_dim, kv_rank, rot_dims, freq, mag, tok_slot, tok_pos) -> None:
+def latent_q_rotate(q_abs, q, n_heads, dim, rot_dim, kv_rank, rot_dims, freq, mag, tok_slot, tok_pos, interleaved=False) -> None:
     """q [T, heads * (dim + rot_dim)]: every head's last rot_dim elements, rotated, go to q_abs
     [T, heads * (kv_rank + rot_dim)] behind the head's first kv_rank elements."""
     check(library().qs_latent_q_rotate(ptr(q_abs), q_abs.stride(0), ptr(q), q.stride(0), dtype_code(q), int(n_heads),
                                        int(dim), int(rot_dim), int(kv_rank), int(rot_dims), ptr(freq), float(mag),
-                                       _int32(tok_slot, "tok_slot"), _int32(tok_pos, "tok_pos"), q.shape[0], stream()))
+                                       _int32(tok_slot, "tok_slot"), _int32(tok_pos, "tok_pos"), q.shape[0],
+                                       int(bool(interleaved)), stream()))
 
 
 def head_linear(out, x, w, n_heads: int) -> None:
@@ -691,9 +712,10 @@ def head_products(out, x, w, n_heads: int) -> None:
 
 # ------------------------------------------------------------------------------- routed experts
 
-def moe_route(z, correction, n_experts, top, groups, keep, scale, gate_col=-1):
+def moe_route(z, correction, n_experts, top, groups, keep, scale, gate_col=-1, scores="sigmoid", group_score="top2"):
     """z float32 [T, >= n_experts] router logits.  Returns (idx int32 [T, top], weights float32 [T, top], shared gate
-    float32 [T] = sigmoid(z[:, gate_col]) or None): see csrc/moe.cu for the rule."""
+    float32 [T] = sigmoid(z[:, gate_col]) or None): see csrc/moe.cu for the rule.  `scores`: "sigmoid" or "softmax" (over
+    all experts); `group_score`: "top2" (the sum of a group's two largest) or "max"; `correction` may be None."""
     T = z.shape[0]
     if z.dtype != torch.float32 or z.stride(1) != 1:
         raise QStreamError(QsError.INVALID_INPUT, "moe_route: router logits must be float32 rows")
@@ -701,13 +723,16 @@ def moe_route(z, correction, n_experts, top, groups, keep, scale, gate_col=-1):
     wts = torch.empty((T, top), dtype=torch.float32, device=z.device)
     gate = torch.empty((T,), dtype=torch.float32, device=z.device) if gate_col >= 0 else None
     check(library().qs_moe_route(ptr(idx), ptr(wts), ptr(gate), ptr(z), z.stride(0), ptr(correction), _code(correction), T,
-                                 int(n_experts), int(top), int(groups), int(keep), float(scale), int(gate_col), stream()))
+                                 int(n_experts), int(top), int(groups), int(keep), float(scale), int(gate_col),
+                                 {"sigmoid": 0, "softmax": 1}[scores], {"top2": 0, "max": 1}[group_score], stream()))
     return idx, wts, gate
 
 
-def moe_experts_indirect(x, w_up, w_down, idx, wts, tok_slot, activation, add=None, add_scale=None) -> torch.Tensor:
+def moe_experts_indirect(x, w_up, w_down, idx, wts, tok_slot, activation, add=None, add_scale=None, glu=None) -> torch.Tensor:
     """sum_j wts[t, j] W_down[idx[t, j]] act(W_up[idx[t, j]] x[t]) (+ add[t] * add_scale[t]) in float32 [T, D]; every
-    pair finds its expert's matrices (w_up [E, F, D], w_down [E, D, F]) on the device: for steps of few tokens."""
+    pair finds its expert's matrices (w_up [E, F, D], w_down [E, D, F]) on the device: for steps of few tokens.
+    `glu` = (limit, alpha, shift): gated experts, w_up [E, 2 F, D] holding an expert's gate rows above its up rows; the
+    hidden vector is `clamped_glu` of the two halves."""
     T, D, ldx = _rows(x)
     E, F, _ = w_up.shape
     top = idx.shape[1]
@@ -716,7 +741,10 @@ def moe_experts_indirect(x, w_up, w_down, idx, wts, tok_slot, activation, add=No
     hidden = torch.empty((T * top, F), dtype=x.dtype, device=x.device)
     out = torch.empty((T, D), dtype=torch.float32, device=x.device)
     check(library().qs_moe_expert_up(ptr(hidden), F, ptr(x), ldx, ptr(w_up), dtype_code(x), _int32(idx, "idx"),
-                                     _int32(tok_slot, "tok_slot"), T, top, D, F, ACTIVATIONS[activation], stream()))
+                                     _int32(tok_slot, "tok_slot"), T, top, D, F, ACTIVATIONS[None if glu else activation], stream()))
+    if glu:
+        hidden = clamped_glu(hidden, *glu)
+        F = F // 2
     check(library().qs_moe_expert_down(ptr(out), D, ptr(hidden), F, ptr(w_down), dtype_code(x), _int32(idx, "idx"), ptr(wts),
                                        _int32(tok_slot, "tok_slot"), ptr(add), _code(add),
                                        add.stride(0) if add is not None else 0, ptr(add_scale), T, top, D, F, stream()))

@@ -13,6 +13,9 @@
 //       (q, k, v arrive ready: activated, normed, scaled; several heads may share one head of q and k).  A column of S
 //       does not meet the others, so the threads of a column pair take S'^T k, S'^T q and k.q in one round of
 //       shuffles, and o_t = S'^T q + u_t (k.q).  In order only (PHASE 0).
+//   gated linear attention with a decay per token and key channel ("gla"):
+//       S_t = diag(w_t) S_{t-1} + k_t v_t^T,   o_t = S_t^T (q_t * q_scale),   w_t = sigmoid(z_t)^decay_scale
+//       (the decay acts before the token's own output, where "wkv" applies it after)
 //
 // The state lives in 32-bit, per slot as [heads][dv][dk] (a column of S is contiguous), starts at zero and is
 // read at the start of a step and written back at its end; everything between the projections and the output is
@@ -30,6 +33,8 @@ constexpr int TILE = 16;            // tokens staged in shared memory at a time
 
 // Which rows a thread owns: groups of four consecutive rows, dealt to the KS threads of a column in turn, so that
 // the threads' 16-byte accesses to a column of the state and to a token's q and k lie side by side.
+__device__ __forceinline__ float log_sigmoid_f32(float z) { return z >= 0.f ? -log1pf(expf(-z)) : z - log1pf(expf(z)); }
+
 __device__ __forceinline__ int row_of(int ks, int ks_log2, int r) { return 4 * (ks + ((r >> 2) << ks_log2)) + (r & 3); }
 
 // PHASE 0: a sequence's tokens in order from the state its slot holds, which is written back at the end.
@@ -48,14 +53,15 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
                   float* __restrict__ state, size_t slot_stride,
                   const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot, int n_seq, int T_rows,
                   int H, int dk, int dv, int ks_log2, int cols, int in_act, int vec,
-                  const float* __restrict__ ga, const float* __restrict__ gb, size_t ldg, float q_scale, int qk_group) {
-    constexpr bool WKV = MODE == 1, GATED = MODE == 2, DELTA = MODE == 3;
+                  const float* __restrict__ ga, const float* __restrict__ gb, size_t ldg, float q_scale, int qk_group,
+                  float decay_scale) {
+    constexpr bool WKV = MODE == 1, GATED = MODE == 2, DELTA = MODE == 3, GLA = MODE == 4;
     extern __shared__ float smem[];
     const int KS = 1 << ks_log2, dkp = KS * RK;
     float* sq = smem;                                   // [TILE][dkp]
     float* sk = sq + TILE * dkp;                        // [TILE][dkp]
     float* sw = sk + TILE * dkp;                        // [TILE][dkp]   (WKV only)
-    float* sv = sw + (WKV || DELTA ? TILE * dkp : 0);   // [TILE][cols]
+    float* sv = sw + (WKV || DELTA || GLA ? TILE * dkp : 0);   // [TILE][cols]
     float* carry = sv + TILE * cols;                    // [dkp]         (PHASE 3: the decay from the chunk's start on)
     float* sa = carry + dkp;                            // [TILE]        (GATED: the tokens' decays)
     const int dvv = GATED ? dv - 1 : dv;                // columns that v holds per head: the gated form adds one of ones
@@ -104,7 +110,7 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
         for (int j = 0; j < 4; ++j)
             u[4 * r4 + j] = (WKV && PHASE != 3 && i + j < dk) ? load_as_f32(bonus, bonus_dtype, (size_t)h * dk + i + j) : 0.f;
     }
-    const float decay = (WKV || GATED) ? 0.f : head_decay[h];
+    const float decay = (WKV || GATED || GLA) ? 0.f : head_decay[h];
     if (PHASE == 3)
         for (int i = tid; i < dkp; i += blockDim.x) carry[i] = 1.0f;
 
@@ -123,7 +129,7 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
                     const size_t row = (size_t)(base + tt);
                     qraw[tt] = q[row * ldq + hq * dk + i];
                     if (PHASE != 3) kraw[tt] = k[row * ldk + hq * dk + i];
-                    if (WKV || DELTA) draw[tt] = dlog[row * ldd + h * dk + i];
+                    if (WKV || DELTA || GLA) draw[tt] = dlog[row * ldd + h * dk + i];
                     if (GATED) draw[tt] = (PHASE == 3 ? ga : gb)[row * ldg + h];
                 }
             }
@@ -137,16 +143,18 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
                         if (PHASE != 3) kv = apply_activation(to_f32(kraw[tt]), in_act);
                         if (WKV) wv = expf(-expf(draw[tt]));
                         if (DELTA) wv = draw[tt];
+                        if (GLA) wv = expf(log_sigmoid_f32(draw[tt]) * decay_scale);
                         if (!WKV && !DELTA) qv *= q_scale;      // a constant factor on q (or, the sums being bilinear, on k)
                         if (GATED && PHASE != 3) kv *= draw[tt];
                     }
                     if (PHASE == 3) {
                         if (WKV) { qv *= run; run *= wv; }
+                        else if (GLA) { run *= wv; qv *= run; }
                         else if (GATED) { run *= (i < dk ? draw[tt] : 0.f); qv *= run; }
                         else { run *= decay; qv *= run; }
                     } else {
                         sk[tt * dkp + i] = kv;
-                        if (WKV || DELTA) sw[tt * dkp + i] = wv;
+                        if (WKV || DELTA || GLA) sw[tt * dkp + i] = wv;
                     }
                     sq[tt * dkp + i] = qv;
                 }
@@ -223,7 +231,7 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
                     const float4 kk = k4[r4 << ks_log2];
                     const float ka[4] = {kk.x, kk.y, kk.z, kk.w};
                     float wa[4] = {0.f, 0.f, 0.f, 0.f};
-                    if (WKV) { const float4 ww = w4[r4 << ks_log2]; wa[0] = ww.x; wa[1] = ww.y; wa[2] = ww.z; wa[3] = ww.w; }
+                    if (WKV || GLA) { const float4 ww = w4[r4 << ks_log2]; wa[0] = ww.x; wa[1] = ww.y; wa[2] = ww.z; wa[3] = ww.w; }
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const int r = r4 * 4 + j;
@@ -233,6 +241,11 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
                             acc1 = fmaf(qa[j], fmaf(u[r], kv1, S1[r]), acc1);
                             S0[r] = fmaf(wa[j], S0[r], kv0);
                             S1[r] = fmaf(wa[j], S1[r], kv1);
+                        } else if (GLA) {
+                            S0[r] = fmaf(wa[j], S0[r], kv0);
+                            S1[r] = fmaf(wa[j], S1[r], kv1);
+                            acc0 = fmaf(qa[j], S0[r], acc0);
+                            acc1 = fmaf(qa[j], S1[r], acc1);
                         } else {
                             const float dec = GATED ? sa[tt] : decay;
                             S0[r] = fmaf(dec, S0[r], kv0);
@@ -276,15 +289,19 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
 }
 
 // The decay of every key channel over a whole chunk: exp(-sum_t exp(dlog[t])) (the product of the tokens' decays),
+// the product of sigmoid(dlog[t])^sigmoid_power where that power is given,
 // or decay_h ^ tokens for a fixed decay per head.  chunk_decay [chunks][H * dk].
 __global__ void chunk_decay_kernel(float* __restrict__ chunk_decay, const float* __restrict__ dlog, size_t ldd,
                                    const float* __restrict__ head_decay, const int32_t* __restrict__ chunk_start,
-                                   int n, int dk, const float* __restrict__ ga, size_t ldg) {
+                                   int n, int dk, const float* __restrict__ ga, size_t ldg, float sigmoid_power) {
     const int c = blockIdx.x;
     const int t0 = chunk_start[c], t1 = chunk_start[c + 1];
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x) {
         float a;
-        if (dlog) {
+        if (dlog && sigmoid_power > 0.f) {              // w = sigmoid(z)^power per token: the product, token by token
+            a = 1.0f;
+            for (int t = t0; t < t1; ++t) a *= expf(log_sigmoid_f32(dlog[(size_t)t * ldd + i]) * sigmoid_power);
+        } else if (dlog) {
             float sum = 0.f;
             for (int t = t0; t < t1; ++t) sum += expf(dlog[(size_t)t * ldd + i]);
             a = expf(-sum);
@@ -434,8 +451,8 @@ int launch_scan(int mode, int phase, float* o, long long ldo, const void* q, lon
                 const void* v, long long ldv, const float* dlog, long long ldd, const float* head_decay, const void* bonus,
                 int bonus_dtype, float* state, long long slot_stride, const int32_t* seq_start, const int32_t* seq_slot,
                 int n_seq, int T_rows, int H, int dk, int dv, int in_act, const float* ga, const float* gb, long long ldg,
-                float q_scale, int qk_group, cudaStream_t stream) {
-    const bool wkv = mode == 1 || mode == 3;            // a decay per token and key channel, staged beside q and k
+                float q_scale, int qk_group, float decay_scale, cudaStream_t stream) {
+    const bool wkv = mode == 1 || mode == 3 || mode == 4;            // a decay per token and key channel, staged beside q and k
     int ks_log2 = 0;
     while ((RK << ks_log2) < dk) ++ks_log2;
     const int KS = 1 << ks_log2;
@@ -458,8 +475,9 @@ int launch_scan(int mode, int phase, float* o, long long ldo, const void* q, lon
     if (e == cudaSuccess) e = qs_launch_dependent(state_scan_kernel<TI, MODE, PHASE>, grid, dim3(threads), smem, stream, o, (size_t)ldo, \
         (const TI*)q, (size_t)ldq, (const TI*)k, (size_t)ldk, (const TI*)v, (size_t)ldv, dlog, (size_t)ldd, head_decay, bonus, \
         bonus_dtype, state, (size_t)slot_stride, seq_start, seq_slot, n_seq, T_rows, H, dk, dv, ks_log2, cols, in_act, vec, \
-        ga, gb, (size_t)ldg, q_scale, qk_group); } while (0)
+        ga, gb, (size_t)ldg, q_scale, qk_group, decay_scale); } while (0)
     if (mode == 3) GO(3, 0);
+    else if (mode == 4) { if (phase == 0) GO(4, 0); else if (phase == 1) GO(4, 1); else GO(4, 3); }
     else if (mode == 1) { if (phase == 0) GO(1, 0); else if (phase == 1) GO(1, 1); else GO(1, 3); }
     else if (mode == 2) { if (phase == 0) GO(2, 0); else if (phase == 1) GO(2, 1); else GO(2, 3); }
     else { if (phase == 0) GO(0, 0); else if (phase == 1) GO(0, 1); else GO(0, 3); }
@@ -469,8 +487,6 @@ int launch_scan(int mode, int phase, float* o, long long ldo, const void* q, lon
 }
 
 // ----------------------------------------------------------------------------- mLSTM: gates and output
-
-__device__ __forceinline__ float log_sigmoid_f32(float z) { return z >= 0.f ? -log1pf(expf(-z)) : z - log1pf(expf(z)); }
 
 // The exponential gates of an mLSTM, stabilised by a running maximum m per sequence and head (0 for an empty
 // sequence).  From the raw gate projections (bias included) raw [T, 2 H] = (input | forget):
@@ -713,23 +729,24 @@ QS_API int qs_state_scan(int mode, float* o, long long ldo, const void* q, long 
                          const int32_t* seq_slot, int n_seq, int T_rows, int H, int dk, int dv, int in_act,
                          const int32_t* chunk_start, const int32_t* chunk_ids, int n_chunks, const int32_t* seq_chunk,
                          float* chunk_state, float* chunk_decay, const float* ga, const float* gb, long long ldg,
-                         float q_scale, int qk_group, cudaStream_t stream) {
+                         float q_scale, int qk_group, float decay_scale, cudaStream_t stream) {
     if (n_seq == 0 || T_rows == 0) return QS_OK;
     QS_REQUIRE(n_seq > 0 && T_rows > 0 && H > 0 && dk > 0 && dv > 0, "state_scan: bad sizes");
     QS_REQUIRE(dk <= 16 * RK, "state_scan: %d key channels per head above %d", dk, 16 * RK);
     QS_REQUIRE(H <= 65535, "state_scan: %d heads exceed the grid", H);
     QS_REQUIRE(mode == 0 ? head_decay != nullptr : mode == 1 ? (dlog && bonus) : mode == 2 ? (ga && gb && dv > 1)
-               : (mode == 3 && dlog && gb && !chunk_start), "state_scan: mode %d lacks its operands", mode);
+               : mode == 4 ? (dlog && decay_scale > 0.f) : (mode == 3 && dlog && gb && !chunk_start),
+               "state_scan: mode %d lacks its operands", mode);
     if (qk_group < 1) qk_group = 1;
     QS_REQUIRE(mode == 3 ? H % qk_group == 0 : qk_group == 1, "state_scan: %d heads in groups of %d", H, qk_group);
     QS_REQUIRE(dtype == QS_F32 || dtype == QS_BF16, "state_scan: unknown dtype %d", dtype);
-    const bool wkv = mode == 1;
+    const bool wkv = mode == 1 || mode == 4;
     (void)wkv;
 #define SCAN(PHASE, STATE, STRIDE, STARTS, SLOTS, N) (dtype == QS_F32 \
         ? launch_scan<float>(mode, PHASE, o, ldo, q, ldq, k, ldk, v, ldv, dlog, ldd, head_decay, bonus, bonus_dtype, STATE, STRIDE, \
-                             STARTS, SLOTS, N, T_rows, H, dk, dv, in_act, ga, gb, ldg, q_scale, qk_group, stream) \
+                             STARTS, SLOTS, N, T_rows, H, dk, dv, in_act, ga, gb, ldg, q_scale, qk_group, decay_scale, stream) \
         : launch_scan<__nv_bfloat16>(mode, PHASE, o, ldo, q, ldq, k, ldk, v, ldv, dlog, ldd, head_decay, bonus, bonus_dtype, STATE, \
-                                     STRIDE, STARTS, SLOTS, N, T_rows, H, dk, dv, in_act, ga, gb, ldg, q_scale, qk_group, stream))
+                                     STRIDE, STARTS, SLOTS, N, T_rows, H, dk, dv, in_act, ga, gb, ldg, q_scale, qk_group, decay_scale, stream))
     if (!chunk_start) return SCAN(0, state, slot_stride, seq_start, seq_slot, n_seq);
     QS_REQUIRE(n_chunks > 0 && chunk_ids && seq_chunk && chunk_state && chunk_decay, "state_scan: chunks without their scratch");
     const long long per_chunk = (long long)H * dv * dk;
@@ -738,7 +755,8 @@ QS_API int qs_state_scan(int mode, float* o, long long ldo, const void* q, long 
     const int n = H * dk;
     chunk_decay_kernel<<<dim3(n_chunks, (n + 127) / 128), 128, 0, stream>>>(chunk_decay, wkv ? dlog : nullptr, (size_t)ldd,
                                                                             head_decay, chunk_start, n, dk,
-                                                                            mode == 2 ? ga : nullptr, (size_t)ldg);
+                                                                            mode == 2 ? ga : nullptr, (size_t)ldg,
+                                                                            mode == 4 ? decay_scale : 0.f);
     if ((rc = qs_check_launch("state_scan chunk decay")) != QS_OK) return rc;
     int by = (int)((per_chunk + 255) / 256);
     if (by > 1024) by = 1024;

@@ -80,7 +80,8 @@ __device__ __forceinline__ float2 row_statistic(const float* row, int D, float e
     return make_float2(mean, 1.0f / sqrtf(var + eps));
 }
 
-// With y: x <- x + norm(y) * wy (wy null: x + y), written back in x's type.  With h_out: h = norm(x) * w.
+// With y: x <- x + norm(y) * wy (wy null: x + y), written back in x's type.  With h_out: h = norm(x) * w, or, without
+// w, x itself in h's type (a sublayer that reads the stream as it is).
 // h_out may be x itself (a norm in place).  A thread reads back only what it wrote to `row`.
 template <typename TX, typename TY, typename TH>
 __global__ void branch_norm_kernel(TH* h_out, size_t ldh, TX* x, size_t ldx, const TY* __restrict__ y, size_t ldy,
@@ -105,8 +106,12 @@ __global__ void branch_norm_kernel(TH* h_out, size_t ldh, TX* x, size_t ldx, con
         for (int i = threadIdx.x; i < D; i += blockDim.x) row[i] = to_f32(xr[i]);
     }
     if (!h_out) return;
-    const float2 st = row_statistic(row, D, eps, center, scratch);
     TH* dst = h_out + (size_t)blockIdx.x * ldh;
+    if (!w) {
+        for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = from_f32<TH>(row[i]);
+        return;
+    }
+    const float2 st = row_statistic(row, D, eps, center, scratch);
     for (int i = threadIdx.x; i < D; i += blockDim.x)
         dst[i] = from_f32<TH>((row[i] - st.x) * st.y * load_as_f32(w, w_dtype, i));
 }
@@ -130,11 +135,12 @@ int launch_branch_norm(void* h_out, long long ldh, void* x, long long ldx, const
 // ----------------------------------------------------------------------------- gated group norm
 
 // One block per row.  group == n: one norm over the row (block sum).  0 < group < n: a warp per group, groups dealt
-// to the warps in turn.  group == 0: no norm.  Then * w[c] (if given) * act(gate[c]) (if given).
+// to the warps in turn.  group == 0: no norm.  Then * w[c] (if given) * act(gate[c / gate_span]) (if given; a span
+// above 1 is one gate value for that many neighbouring elements, a head's say).
 template <typename TI, typename TG, typename TO>
 __global__ void gated_group_norm_kernel(TO* __restrict__ out, size_t ldo, const TI* __restrict__ o, size_t ldi,
                                         const void* __restrict__ w, int w_dtype, const TG* __restrict__ gate, size_t ldg,
-                                        int gate_act, int n, int group, float eps) {
+                                        int gate_act, int n, int group, float eps, int gate_span) {
     extern __shared__ float rstd_of[];               // one per group (at least one)
     __shared__ float scratch[33];
     grid_dep_launch();
@@ -160,19 +166,19 @@ __global__ void gated_group_norm_kernel(TO* __restrict__ out, size_t ldo, const 
         float v = to_f32(src[i]);
         if (group > 0) v *= rstd_of[i / group];
         if (w) v *= load_as_f32(w, w_dtype, i);
-        if (gate) v *= apply_activation(to_f32(gate[(size_t)blockIdx.x * ldg + i]), gate_act);
+        if (gate) v *= apply_activation(to_f32(gate[(size_t)blockIdx.x * ldg + (gate_span > 1 ? i / gate_span : i)]), gate_act);
         dst[i] = from_f32<TO>(v);
     }
 }
 
 template <typename TI, typename TG, typename TO>
 int launch_gated(void* out, long long ldo, const void* o, long long ldi, const void* w, int w_dtype, const void* gate,
-                 long long ldg, int gate_act, int rows, int n, int group, float eps, cudaStream_t stream) {
+                 long long ldg, int gate_act, int rows, int n, int group, float eps, int gate_span, cudaStream_t stream) {
     const int n_groups = group > 0 ? n / group : 1;
     const int threads = n >= 2048 ? 256 : 128;
     cudaError_t e = qs_launch_dependent(gated_group_norm_kernel<TI, TG, TO>, dim3(rows), dim3(threads),
                                         (size_t)n_groups * sizeof(float), stream, (TO*)out, (size_t)ldo, (const TI*)o,
-                                        (size_t)ldi, w, w_dtype, (const TG*)gate, (size_t)ldg, gate_act, n, group, eps);
+                                        (size_t)ldi, w, w_dtype, (const TG*)gate, (size_t)ldg, gate_act, n, group, eps, gate_span);
     if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "gated_group_norm: %s", cudaGetErrorString(e));
     return qs_check_launch("gated_group_norm");
 }
@@ -204,6 +210,21 @@ __global__ void gated_act_kernel(T* __restrict__ out, size_t ldo, const T* __res
         const float a = to_f32(ab[r * ldi + c]), b = to_f32(ab[r * ldi + F + c]);
         out[r * ldo + c] = from_f32<T>(apply_activation(a, act) * b);
     }
+}
+
+// The clamped gated unit of two halves [a | b]: g = min(a, limit), u = clamp(b, -limit, limit),
+// out = g * sigmoid(alpha * g) * (u + shift); 32-bit arithmetic, rounded once.  limit <= 0: no clamp.
+template <typename T>
+__global__ void clamped_glu_kernel(T* __restrict__ out, size_t ldo, const T* __restrict__ ab, size_t ldi, int F, float limit,
+                                   float alpha, float shift) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const size_t r = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= F) return;
+    float g = to_f32(ab[r * ldi + c]), u = to_f32(ab[r * ldi + F + c]);
+    if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+    out[r * ldo + c] = from_f32<T>(g * sigmoid_f32(alpha * g) * (u + shift));
 }
 
 // x <- act(x), in 32-bit, rounded once: for activations that the matrix products' epilogues do not offer.
@@ -302,7 +323,6 @@ QS_API int qs_branch_norm(void* h_out, int h_dtype, long long ldh, void* x, int 
     if (rows == 0) return QS_OK;
     QS_REQUIRE(rows > 0 && D > 0, "branch_norm: bad sizes rows=%d D=%d", rows, D);
     QS_REQUIRE(h_out || y, "branch_norm: nothing to do");
-    QS_REQUIRE(!h_out || w, "branch_norm: a norm without a weight");
     QS_REQUIRE((size_t)D * sizeof(float) <= 200 * 1024, "branch_norm: width %d does not fit one block's shared memory", D);
     typedef __nv_bfloat16 bf16;
     if (!y) y_dtype = x_dtype;
@@ -319,13 +339,14 @@ QS_API int qs_branch_norm(void* h_out, int h_dtype, long long ldh, void* x, int 
 
 QS_API int qs_gated_group_norm(void* out, int out_dtype, long long ldo, const void* o, int o_dtype, long long ldi,
                                const void* w, int w_dtype, const void* gate, int gate_dtype, long long ldg,
-                               int gate_act, int rows, int n, int group, float eps, cudaStream_t stream) {
+                               int gate_act, int rows, int n, int group, float eps, int gate_span, cudaStream_t stream) {
     if (rows == 0) return QS_OK;
     QS_REQUIRE(rows > 0 && n > 0 && group >= 0 && (group == 0 || n % group == 0),
                "gated_group_norm: bad sizes rows=%d n=%d group=%d", rows, n, group);
+    QS_REQUIRE(gate_span >= 1 && n % gate_span == 0, "gated_group_norm: %d elements in spans of %d", n, gate_span);
     typedef __nv_bfloat16 bf16;
     if (!gate) gate_dtype = out_dtype;
-#define GO(TI, TG, TO) return launch_gated<TI, TG, TO>(out, ldo, o, ldi, w, w_dtype, gate, ldg, gate_act, rows, n, group, eps, stream)
+#define GO(TI, TG, TO) return launch_gated<TI, TG, TO>(out, ldo, o, ldi, w, w_dtype, gate, ldg, gate_act, rows, n, group, eps, gate_span, stream)
     if (o_dtype == QS_F32 && gate_dtype == QS_F32 && out_dtype == QS_F32) GO(float, float, float);
     if (o_dtype == QS_F32 && gate_dtype == QS_BF16 && out_dtype == QS_BF16) GO(float, bf16, bf16);
     if (o_dtype == QS_F32 && gate_dtype == QS_F32 && out_dtype == QS_BF16) GO(float, float, bf16);
@@ -359,6 +380,26 @@ QS_API int qs_gated_act(void* out, long long ldo, const void* ab, long long ldi,
     }
     if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "gated_act: %s", cudaGetErrorString(e));
     return qs_check_launch("gated_act");
+}
+
+QS_API int qs_clamped_glu(void* out, long long ldo, const void* ab, long long ldi, int dtype, int rows, int F, float limit,
+                          float alpha, float shift, cudaStream_t stream) {
+    if (rows == 0) return QS_OK;
+    QS_REQUIRE(rows > 0 && F > 0 && ldi >= 2 * (long long)F && ldo >= F, "clamped_glu: bad sizes rows=%d F=%d", rows, F);
+    typedef __nv_bfloat16 bf16;
+    const int threads = F >= 256 ? 256 : 64;
+    const int by = (F + threads - 1) / threads;
+    QS_REQUIRE(by <= 65535, "clamped_glu: %d columns exceed the grid", F);
+    cudaError_t e;
+    if (dtype == QS_F32)
+        e = qs_launch_dependent(clamped_glu_kernel<float>, dim3(rows, by), dim3(threads), 0, stream, (float*)out, (size_t)ldo,
+                                (const float*)ab, (size_t)ldi, F, limit, alpha, shift);
+    else if (dtype == QS_BF16)
+        e = qs_launch_dependent(clamped_glu_kernel<bf16>, dim3(rows, by), dim3(threads), 0, stream, (bf16*)out, (size_t)ldo,
+                                (const bf16*)ab, (size_t)ldi, F, limit, alpha, shift);
+    else return qs_fail(QS_ERR_INVALID_INPUT, "clamped_glu: unknown dtype %d", dtype);
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "clamped_glu: %s", cudaGetErrorString(e));
+    return qs_check_launch("clamped_glu");
 }
 
 QS_API int qs_activate(void* x, long long ld, int dtype, int rows, int n, int act, cudaStream_t stream) {

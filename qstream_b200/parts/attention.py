@@ -12,7 +12,8 @@ with those that an earlier layer computed for the same token (what is cached is 
 from the mixer's input on the concatenated heads (its projection rides in the same product as q, k, v); keys seen
 only inside the query's chunk of positions, or inside a window that also keeps the sequence's first tokens; a learned
 sink per head in the softmax's denominator; two attention maps per head over the same values, joined as a difference
-with a unit RMS per head (differential attention).
+with a unit RMS per head (differential attention); one RMS norm over the whole q and the whole k projection before the
+heads are split; values that are the keys as projected (no W_v); a sink of a fixed score without a tensor.
 """
 from __future__ import annotations
 
@@ -41,7 +42,12 @@ class Attention(Mixer):
             d.update({n: TensorDecl((spec.head_dim,), "bias") for n in ("lq1", "lk1", "lq2", "lk2")})
         if not spec.shares_cache:
             d["k"] = TensorDecl((hkv, spec.width))
-            d["v"] = TensorDecl((hv, spec.width))
+            if not getattr(spec, "values_from_keys", False):
+                d["v"] = TensorDecl((hv, spec.width))
+        if getattr(spec, "qk_norm", None):
+            d["q_norm"] = TensorDecl((hq,), "norm_weight")
+            if not spec.shares_cache:
+                d["k_norm"] = TensorDecl((hkv,), "norm_weight")
         if spec.qkv_bias:
             d["q_bias"] = TensorDecl((hq,), "bias")
             if not spec.shares_cache:
@@ -65,7 +71,13 @@ class Attention(Mixer):
                                f"attention kernels take even head sizes up to 512, not {spec.head_dim} / {spec.value_dim}")
         if spec.value_mix not in (None, "first", "blend") or (spec.value_mix and spec.shares_cache):
             raise QStreamError(QsError.INVALID_MODEL, f"attention: value_mix '{spec.value_mix}' does not fit")
-        names = ["q"] if spec.shares_cache else ["q", "k", "v"]
+        self.values_from_keys = bool(getattr(spec, "values_from_keys", False))
+        self.qk_norm = getattr(spec, "qk_norm", None)
+        if self.qk_norm not in (None, "whole"):
+            raise QStreamError(QsError.UNSUPPORTED_ARCH, f"attention: no norm of q and k of kind '{self.qk_norm}'")
+        if self.values_from_keys and (spec.value_dim != getattr(spec, "maps", 1) * spec.head_dim or spec.value_mix or spec.qkv_bias):
+            raise QStreamError(QsError.INVALID_MODEL, "attention: values taken from the keys have the keys' size, no bias and no blend")
+        names = ["q"] if spec.shares_cache else (["q", "k"] if self.values_from_keys else ["q", "k", "v"])
         mats = [tensors[n] for n in names] + ([tensors["gate"]] if spec.gate else [])
         if len({m.dtype for m in mats}) != 1:
             raise QStreamError(QsError.INVALID_MODEL, "q/k/v projections are stored in different types")
@@ -87,6 +99,12 @@ class Attention(Mixer):
         if self.chunk and spec.window:
             raise QStreamError(QsError.INVALID_MODEL, "attention: chunks and a window exclude each other")
         self.sink = tensors["sink"].float().contiguous() if getattr(spec, "sink", False) else None
+        if getattr(spec, "fixed_sink", None) is not None:
+            if self.sink is not None:
+                raise QStreamError(QsError.INVALID_MODEL, "attention: a learned sink and a fixed one exclude each other")
+            self.sink = torch.full((spec.n_heads,), float(spec.fixed_sink), dtype=torch.float32, device=runtime.device)
+        self.q_norm = tensors["q_norm"] if self.qk_norm else None
+        self.k_norm = tensors["k_norm"] if self.qk_norm and not spec.shares_cache else None
         # which of the kernels' options only the generic kernel offers
         self.masked = bool(self.chunk or self.keep_first or self.sink is not None or self.maps > 1)
         self.lam = 0.0
@@ -128,6 +146,8 @@ class Attention(Mixer):
         hq, hkv, hv = s.n_heads * self.maps * s.head_dim, s.n_kv_heads * self.maps * s.head_dim, s.n_kv_heads * s.value_dim
         qkv = linear(h, self.w_qkv, self.b_qkv)
         q = qkv[:, :hq]
+        if self.qk_norm:                                # one norm over all heads' rows at once, statistics in 32-bit
+            q = ops.rmsnorm(q, self.q_norm, float(s.eps), out_dtype=q.dtype)
         if s.gate and out is not None:
             raise QStreamError(QsError.INVALID_INPUT, "attention: a gated mixer writes its own output")
         table = getattr(self.position, "fused_table", None) if self.position is not None else None
@@ -144,7 +164,9 @@ class Attention(Mixer):
                                    step.status, settled=True, half_layout=half)
         else:
             k = qkv[:, hq:hq + hkv]
-            v = qkv[:, hq + hkv:hq + hkv + hv]
+            v = k if self.values_from_keys else qkv[:, hq + hkv:hq + hkv + hv]     # the keys as projected: the kernel only reads k
+            if self.qk_norm:
+                k = ops.rmsnorm(k, self.k_norm, float(s.eps), out_dtype=k.dtype)
             v_first = None
             if s.value_mix == "first":
                 step.scratch["value_mix"] = v               # later layers of this step blend their values with these
@@ -192,19 +214,20 @@ class Attention(Mixer):
         return o
 
 
-def attend(q, spec, step, view, out=None, gate=None):
+def attend(q, spec, step, view, out=None, gate=None, sink=None):
     """Pick the attention kernel for this step: decode and prefill have their own
     bfloat16 kernels; the generic kernel takes every other case.  `gate` [T, heads * value_dim]: the result
-    times sigmoid(gate), in the bfloat16 kernels' last stage or by a kernel of its own."""
+    times sigmoid(gate), in the bfloat16 kernels' last stage or by a kernel of its own.  `sink` (float32, one per
+    query head): exp(sink) joins each softmax's denominator."""
     b = step.batch
     if q.dtype == torch.bfloat16:
         from ..csrc import attention_bf16
-        done = attention_bf16.attend(q, spec, step, view, out, gate)
+        done = attention_bf16.attend(q, spec, step, view, out, gate, sink=sink)
         if done is not None:
             return done
     o = ops.attention(q, spec.n_heads, spec.n_kv_heads, spec.head_dim, spec.scale, spec.window,
                       b.tok_slot, b.tok_pos, view.page_table, view.page_tokens, view.k, view.v,
-                      step.status, out=out, v_head_dim=spec.value_dim, softcap=spec.softcap)
+                      step.status, out=out, v_head_dim=spec.value_dim, softcap=spec.softcap, sink=sink)
     if gate is not None:
         o = ops.gated_group_norm(o, 0, None, gate, "sigmoid", 0.0, o.dtype)
     return o

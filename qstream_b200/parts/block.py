@@ -262,6 +262,47 @@ class SandwichBlock(Arrangement):
         return x
 
 
+class PostNormBlock(Arrangement):
+    """The sublayers read the stream itself and a norm meets their results only: x += norm_1(mixer(x));
+    x += norm_2(ffn(x)), with the residual stream x in 32-bit whatever the engine's type and updated in place; a layer
+    may have no feed-forward.  The branches arrive in 32-bit from their last product.  The norm of a branch, its
+    addition to x and the copy of the new x in the engine's type that the next sublayer reads are one kernel, also
+    across layers: a layer leaves its last branch pending (`step.pending`) for the next layer's read.  Norms must
+    offer `read_update(x, branch, branch_norm)`, `read` and `add_normed` (the stream norm does)."""
+    norm_names = ("post_input",)
+    takes_pending = True
+
+    def __init__(self, spec, parts, runtime):
+        super().__init__(spec, parts, runtime)
+        import inspect
+        import torch
+        if self.ffn is not None and "post_ffn" not in self.norms:
+            raise QStreamError(QsError.INVALID_MODEL, "a post-norm layer with a feed-forward needs the norm 'post_ffn'")
+        self.wide = torch.float32
+        self._typed = {id(p): "out_dtype" in inspect.signature(p.forward).parameters for p in (self.mixer, self.ffn) if p}
+
+    part_specs = classmethod(ScaledResidualBlock.part_specs.__func__)      # a layer may lack its feed-forward here too
+    build = classmethod(ScaledResidualBlock.build.__func__)
+
+    def _wide(self, part):
+        return {"out_dtype": self.wide} if self._typed[id(part)] else {}
+
+    def forward(self, x, step, cache_id):
+        before, step.pending = step.pending, None
+        last = self.norms["post_input"]
+        if isinstance(before, PendingNormedUpdate):
+            h = last.read_update(x, before.branch, before.norm)
+        else:
+            h = last.read(before.apply(x) if before is not None else x)
+        y = self.mixer.forward(h, step, cache_id, **self._wide(self.mixer))
+        if self.ffn is not None:
+            h = last.read_update(x, y, last)
+            y = self.ffn.forward(h, step, **self._wide(self.ffn))
+            last = self.norms["post_ffn"]
+        step.pending = PendingNormedUpdate(y, last)
+        return x
+
+
 class HyperConnection(Part):
     """The tensors with which one sublayer meets a residual stream kept in several copies: the weights of the read
     (`in`), of the write (`out`), the matrix that mixes the copies (`mix`, [from, to]) and the vector that scales the
@@ -388,6 +429,7 @@ class HyperBlock(Arrangement):
 register("arrangement", "hyper", HyperBlock)
 register("connection", "hyper_connection", HyperConnection)
 register("arrangement", "parallel", ParallelBlock)
+register("arrangement", "post_norm", PostNormBlock)
 register("arrangement", "sandwich", SandwichBlock)
 register("arrangement", "sequential", SequentialBlock)
 register("arrangement", "scaled_residual", ScaledResidualBlock)

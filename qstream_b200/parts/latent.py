@@ -6,6 +6,9 @@ its output W_uv (sum_j p_j c_j): attention with one key head of size kv_rank + r
 first kv_rank elements.  That form runs on the library's own attention kernels (decode, prefill, generic) through
 the paged cache, with keys [c | k_rot] and values c; a layer that shares another's cache reads that entry with its
 own W_uk and W_uv.  Norms, rotation, scores and softmax are 32-bit; the projections run in the engine's type.
+Options of the spec: a learned sink per head in the softmax's denominator; a sigmoid gate per head from the mixer's
+input, whose rows ride in the down projections' product; the rotation's pairing (halves or neighbours) is the
+position part's.
 """
 from __future__ import annotations
 
@@ -37,6 +40,10 @@ class LatentAttention(Mixer):
         if not spec.shares_cache:
             d["dkv"] = TensorDecl((spec.kv_rank + spec.rot_dim, spec.width))
             d["dkv_norm"] = TensorDecl((spec.kv_rank,), "norm_weight")
+        if getattr(spec, "sink", False):
+            d["sink"] = TensorDecl((H,), "bias")
+        if getattr(spec, "head_gate", False):
+            d["g"] = TensorDecl((H, spec.width))
         return d
 
     def __init__(self, spec, tensors, runtime):
@@ -50,7 +57,11 @@ class LatentAttention(Mixer):
             raise QStreamError(QsError.UNSUPPORTED_ARCH, f"latent attention: a latent of {spec.kv_rank} (+ {spec.rot_dim}) exceeds the attention kernels")
         H, dn, r = spec.n_heads, spec.head_dim, spec.kv_rank
         # both down projections read h: one product
-        self.w_down = tensors["dq"] if spec.shares_cache else torch.cat([tensors["dq"], tensors["dkv"]], dim=0).contiguous()
+        self.head_gate = bool(getattr(spec, "head_gate", False))
+        self.sink = tensors["sink"].float().contiguous() if getattr(spec, "sink", False) else None
+        self.interleaved = getattr(spec.position, "layout", "half") == "interleaved"
+        down = [tensors["dq"]] + ([] if spec.shares_cache else [tensors["dkv"]]) + ([tensors["g"]] if self.head_gate else [])
+        self.w_down = torch.cat(down, dim=0).contiguous() if len(down) > 1 else down[0]
         self.q_norm = tensors["dq_norm"]
         self.kv_norm = None if spec.shares_cache else tensors["dkv_norm"]
         self.w_uq = tensors["uq"]
@@ -78,18 +89,22 @@ class LatentAttention(Mixer):
         view = step.kv(cache_id)
         H, dn, dr, dv, r = s.n_heads, s.head_dim, s.rot_dim, s.v_head_dim, s.kv_rank
         d = linear(h, self.w_down)
-        cq = ops.latent_prepare(d[:, :s.q_rank], self.q_norm, s.q_rank, None if s.shares_cache else d[:, s.q_rank:],
+        cq = ops.latent_prepare(d[:, :s.q_rank], self.q_norm, s.q_rank, None if s.shares_cache else d[:, s.q_rank:s.q_rank + r + dr],
                                 self.kv_norm, r, dr, pos.rotary_dim, pos.frequencies, pos.magnitude, s.eps, b.tok_slot,
-                                b.tok_pos, view.page_table, view.page_tokens, view.k, view.v, step.status)
+                                b.tok_pos, view.page_table, view.page_tokens, view.k, view.v, step.status,
+                                interleaved=self.interleaved)
         q = linear(cq, self.w_uq)
         T = q.shape[0]
         q_abs = torch.empty((T, H * (r + dr)), dtype=q.dtype, device=q.device)
-        ops.latent_q_rotate(q_abs, q, H, dn, dr, r, pos.rotary_dim, pos.frequencies, pos.magnitude, b.tok_slot, b.tok_pos)
+        ops.latent_q_rotate(q_abs, q, H, dn, dr, r, pos.rotary_dim, pos.frequencies, pos.magnitude, b.tok_slot, b.tok_pos,
+                            interleaved=self.interleaved)
         few = T <= FEW_TOKENS                   # one launch for all heads; else a product per head, dealt to several streams
         (ops.head_linear if few else ops.head_products)(q_abs, q, self.w_uk_t, H)
-        latent = attend(q_abs, self.as_attention, step, view)
+        latent = attend(q_abs, self.as_attention, step, view, sink=self.sink)
         o = torch.empty((T, H * dv), dtype=q.dtype, device=q.device)
         (ops.head_linear if few else ops.head_products)(o, latent, self.w_uv_heads, H)
+        if self.head_gate:                              # one gate value per head, the product's last H columns
+            o = ops.gated_group_norm(o, 0, None, d[:, d.shape[1] - H:], "sigmoid", 0.0, o.dtype, gate_span=dv)
         return linear(o, self.w_out, None, residuals=residuals, out_dtype=out_dtype)
 
 

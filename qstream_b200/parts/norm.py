@@ -78,6 +78,20 @@ class StreamNorm(Norm):
         ops.branch_norm(x, None, self.eps, self.center, branch=branch, branch_weight=self.weight, want_norm=False)
         return x
 
+    def read(self, x):
+        """The stream as a sublayer without a norm of its own reads it: x in the engine's type (x itself where that is
+        the stream's type; nobody changes x while the sublayer runs)."""
+        if x.dtype == self.runtime.dtype:
+            return x
+        return ops.branch_norm(x, None, self.eps, self.center, out_dtype=self.runtime.dtype)
+
+    def read_update(self, x, branch, branch_norm):
+        """x <- x + branch_norm(branch) (in place), then `read` of the new x, in one kernel."""
+        if x.dtype == self.runtime.dtype:
+            return branch_norm.add_normed(x, branch)
+        return ops.branch_norm(x, None, self.eps, self.center, out_dtype=self.runtime.dtype, branch=branch,
+                               branch_weight=branch_norm.weight)
+
 
 class StreamSumNorm(Norm):
     """The RMS norm of the sum of a residual stream's copies: rows [n, streams * size] in 32-bit, the copies side by

@@ -9,6 +9,10 @@ two-matrix bottleneck whose output d gives the decay w = exp(-exp(d + w0)) per t
     o_t = (S_{t-1} + diag(u) k_t v_t^T)^T r_t,  S_t = diag(w_t) S_{t-1} + k_t v_t^T;
 each head's o is divided by its root mean square, then weight, silu gate, W_o.
 
+`Gla` ("gla"): gated linear attention, S_t = diag(w_t) S_{t-1} + k_t v_t^T, o_t = S_t^T q_t, with a decay per token and
+key channel w = sigmoid(W_a2 W_a1 h + b)^(1 / tau); each head's o gets an RMS norm with a weight shared by the heads,
+then a silu gate and W_o.
+
 `GatedDelta` ("gated_delta"): the delta rule with a decay per token, head and key channel and a step size per token
 and head, behind short causal convolutions on q, k and v.  `PairMixer` ("pair"): two mixers side by side.
 
@@ -186,6 +190,48 @@ class Mlstm(Mixer):
         return linear(y, self.w_out, None, residuals=residuals, out_dtype=out_dtype)
 
 
+class Gla(Mixer):
+    """Gated linear attention.  q, k, v, the gate and the first matrix of the decays' bottleneck are one product in the
+    engine's type; the bottleneck's second matrix (with its bias) gives the decays' logits in 32-bit; the scan takes
+    sigmoid(.)^(1 / tau) of them in 32-bit as it stages a token, decays the state, adds k v^T and reads o (a long prompt:
+    its chunks side by side, joined by a prefix over the chunks' states); the last kernel takes each head's RMS norm,
+    the weight and the silu gate."""
+    captures_any_step = True
+
+    @classmethod
+    def declare(cls, spec):
+        hk, hv, D, R = spec.n_heads * spec.key_dim, spec.n_heads * spec.value_dim, spec.width, spec.decay_rank
+        return {"q": TensorDecl((hk, D)), "k": TensorDecl((hk, D)), "v": TensorDecl((hv, D)), "g": TensorDecl((hv, D)),
+                "o": TensorDecl((D, hv)), "norm": TensorDecl((spec.value_dim,), "norm_weight"),
+                "a1": TensorDecl((R, D)), "a2": TensorDecl((hk, R)), "a2_bias": TensorDecl((hk,), "bias")}
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        if not spec.tau > 0:
+            raise QStreamError(QsError.INVALID_MODEL, f"gla: tau={spec.tau} must be positive")
+        self.w_in = torch.cat([tensors[n] for n in ("q", "k", "v", "g", "a1")], dim=0).contiguous()
+        self.rank = tensors["a1"].shape[0]
+        self.w_a2, self.b_a2 = tensors["a2"], tensors["a2_bias"].float().contiguous()
+        self.w_out = tensors["o"]
+        self.norm = tensors["norm"].repeat(spec.n_heads).contiguous()       # one weight of value_dim, shared by the heads
+
+    def state_need(self):
+        s = self.spec
+        return StateNeed((s.n_heads, s.value_dim, s.key_dim), torch.float32)
+
+    def forward(self, h, step, cache_id, residuals=(), out_dtype=None):
+        s, b = self.spec, step.batch
+        hk, hv = s.n_heads * s.key_dim, s.n_heads * s.value_dim
+        p = linear(h, self.w_in)
+        at = 2 * hk + 2 * hv
+        z = linear(p[:, at:at + self.rank], self.w_a2, self.b_a2, out_dtype=torch.float32)
+        o = ops.state_scan("gla", p[:, :hk], p[:, hk:2 * hk], p[:, 2 * hk:2 * hk + hv], step.state(cache_id),
+                           b.seq_start, b.seq_slot, b.n_seq, s.n_heads, s.key_dim, s.value_dim, decay_logits=z,
+                           decay_power=1.0 / float(s.tau), q_scale=s.key_dim ** -0.5, chunks=scan_chunks(b, h.device))
+        y = ops.gated_group_norm(o, s.value_dim, self.norm, p[:, 2 * hk + hv:at], "silu", s.eps, h.dtype)
+        return linear(y, self.w_out, None, residuals=residuals, out_dtype=out_dtype)
+
+
 class GatedDelta(Mixer):
     """The gated delta rule: S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q per head.  q, k, v and the
     first matrices of the two bottlenecks are one product in the engine's type; the step sizes' projection and the
@@ -287,6 +333,7 @@ class PairMixer(Mixer):
 
 
 register("mixer", "gated_delta", GatedDelta)
+register("mixer", "gla", Gla)
 register("mixer", "pair", PairMixer)
 register("mixer", "lightning", DecayAttention)
 register("mixer", "mlstm", Mlstm)
