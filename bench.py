@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the library on one B200, as one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
-                    [--config gptj6b|codegen2b|codegen16b] [--skip-points] [--per-kernel] [--design lutelorn|fofinex|sefuvik]
+                    [--config gptj6b|codegen2b|codegen16b] [--skip-points] [--per-kernel] [--design lutelorn|fofinex|sefuvik|nutatar]
 
 The default run has GPT-J-6B's layer sizes (28 layers, width 4096, 16 heads of 256, rotary 64,
 inner 16384, vocabulary 50400, 2048 positions) with random bfloat16 weights, a batch of 8
@@ -532,8 +532,8 @@ def main(argv=None) -> int:
     ap.add_argument("--skip-points", action="store_true", help="the timed steps only: no other batch sizes, runs, prefill, e2e")
     ap.add_argument("--per-kernel", action="store_true", help="time each kernel of one layer by itself and print a table")
     ap.add_argument("--prefill-tokens", type=int, default=2048, help="with --per-kernel: tokens of the prompt step")
-    ap.add_argument("--design", default="", choices=["", "lutelorn", "fofinex", "sefuvik"],
-                    help="another model design beside an existing one at equal sizes (lutelorn beside GPT-J, fofinex and sefuvik beside lutelorn): prefill and decode throughput of both and "
+    ap.add_argument("--design", default="", choices=["", "lutelorn", "fofinex", "sefuvik", "nutatar"],
+                    help="another model design beside an existing one at equal sizes (lutelorn beside GPT-J, fofinex and sefuvik beside lutelorn, nutatar beside fofinex): prefill and decode throughput of both and "
                          "the new kernels against their rooflines (the default run is unchanged)")
     args = ap.parse_args(argv)
     if args.impl == "reference":

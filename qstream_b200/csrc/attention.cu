@@ -95,6 +95,74 @@ __global__ void rope_store_kernel(T* __restrict__ q, const T* __restrict__ k, co
     }
 }
 
+// One RMS norm over a token's whole q row (all heads at once) and one over its whole k row, then the rotation and the
+// cache write, in one pass: q[i] <- rot(q[i] * rstd_q * wq[i]) in place, the cache keeps rot(k[i] * rstd_k * wk[i]) and
+// the values as they are (v may be k itself: values that are the keys as projected).  One block per token; statistics,
+// weights and rotation in 32-bit, every result rounded once.  Rows of no sequence (slot < 0) get zeros.
+template <typename T>
+__global__ void norm_rope_store_kernel(T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                                       size_t ldq, size_t ldk, size_t ldv, const void* __restrict__ wq, int wq_dtype,
+                                       const void* __restrict__ wk, int wk_dtype, float eps,
+                                       int n_heads, int n_kv_heads, int dh, int dv, int R,
+                                       const float* __restrict__ cos_sin, int max_pos,
+                                       const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
+                                       const int32_t* __restrict__ page_table, int max_pages, int page_shift,
+                                       T* __restrict__ k_cache, T* __restrict__ v_cache, int32_t* __restrict__ status,
+                                       int half_layout) {
+    __shared__ float scratch[33];
+    grid_dep_launch();
+    grid_dep_wait();
+    const int t = blockIdx.x, tid = threadIdx.x, stride = blockDim.x;
+    const int slot = tok_slot[t];
+    const int nq = n_heads * dh, nk = n_kv_heads * dh;
+    T* qrow = q + (size_t)t * ldq;
+    if (slot < 0) {
+        for (int i = tid; i < nq; i += stride) qrow[i] = from_f32<T>(0.f);
+        return;
+    }
+    const int pos = tok_pos[t];
+    const bool rotate = cos_sin != nullptr && R > 0;
+    if (rotate && (pos < 0 || pos >= max_pos)) { if (tid == 0) atomicExch(status, 1); return; }
+    const float* cs = rotate ? cos_sin + (size_t)pos * R : nullptr;
+    const T* krow = k + (size_t)t * ldk;
+    float sq = 0.f, sk = 0.f;
+    for (int i = tid; i < nq; i += stride) { const float x = to_f32(qrow[i]); sq = fmaf(x, x, sq); }
+    for (int i = tid; i < nk; i += stride) { const float x = to_f32(krow[i]); sk = fmaf(x, x, sk); }
+    const float rq = 1.0f / sqrtf(block_sum(sq, scratch) / (float)nq + eps);
+    const float rk = nk > 0 ? 1.0f / sqrtf(block_sum(sk, scratch) / (float)nk + eps) : 0.f;
+    const int half = dh >> 1, rp = rotate ? R >> 1 : 0;
+    // an item is a pair of elements of one head: a rotated pair while j < R/2, then two plain neighbours
+    for (int e = tid; e < n_heads * half; e += stride) {
+        const int head = e / half, j = e - head * half;
+        const bool turn = j < rp;
+        const int ia = head * dh + ((turn && half_layout) ? j : 2 * j), ib = head * dh + ((turn && half_layout) ? j + rp : 2 * j + 1);
+        const float a = to_f32(qrow[ia]) * rq * load_as_f32(wq, wq_dtype, ia), b = to_f32(qrow[ib]) * rq * load_as_f32(wq, wq_dtype, ib);
+        const float c = turn ? cs[2 * j] : 1.f, sn = turn ? cs[2 * j + 1] : 0.f;
+        qrow[ia] = from_f32<T>(a * c - b * sn);
+        qrow[ib] = from_f32<T>(a * sn + b * c);
+    }
+    if (n_kv_heads == 0) return;
+    const int page = page_table[(size_t)slot * max_pages + (pos >> page_shift)];
+    if (page < 0) { if (tid == 0) atomicExch(status, 2); return; }
+    const int page_tokens = 1 << page_shift;
+    const size_t in_page = (size_t)(pos & (page_tokens - 1));
+    for (int e = tid; e < n_kv_heads * half; e += stride) {
+        const int kvh = e / half, j = e - kvh * half;
+        const bool turn = j < rp;
+        const int la = (turn && half_layout) ? j : 2 * j, lb = (turn && half_layout) ? j + rp : 2 * j + 1;
+        const int ia = kvh * dh + la, ib = kvh * dh + lb;
+        const float a = to_f32(krow[ia]) * rk * load_as_f32(wk, wk_dtype, ia), b = to_f32(krow[ib]) * rk * load_as_f32(wk, wk_dtype, ib);
+        const float c = turn ? cs[2 * j] : 1.f, sn = turn ? cs[2 * j + 1] : 0.f;
+        T* kdst = k_cache + (((size_t)page * n_kv_heads + kvh) * page_tokens + in_page) * dh;
+        kdst[la] = from_f32<T>(a * c - b * sn);
+        kdst[lb] = from_f32<T>(a * sn + b * c);
+    }
+    for (int e = tid; e < n_kv_heads * dv; e += stride) {
+        const int kvh = e / dv, j = e - kvh * dv;
+        v_cache[(((size_t)page * n_kv_heads + kvh) * page_tokens + in_page) * dv + j] = v[(size_t)t * ldv + (size_t)kvh * dv + j];
+    }
+}
+
 // The same for bfloat16 with 16-byte accesses: an item is eight consecutive dims (four rotary pairs).
 // Needs head size and rotary width multiples of 8 and 16-byte aligned rows.
 __device__ __forceinline__ uint4 rotate8(const uint4 raw, const float* __restrict__ cs8) {
@@ -384,6 +452,37 @@ QS_API int qs_rope_store(void* q, const void* k, const void* v, int dtype,
             (const __nv_bfloat16*)v_first, (size_t)ldvf, lam, half_layout);
     else return qs_fail(QS_ERR_INVALID_INPUT, "rope_store: unknown dtype %d", dtype);
     return qs_check_launch("rope_store");
+}
+
+// See norm_rope_store_kernel.  wq [n_heads * dh] and wk [n_kv_heads * dh] are the two norms' weights; n_kv_heads = 0
+// (k, v, the cache null): a layer that projects queries only.
+QS_API int qs_norm_rope_store(void* q, const void* k, const void* v, int dtype, long long ldq, long long ldk, long long ldv,
+                              const void* wq, int wq_dtype, const void* wk, int wk_dtype, float eps, int n_heads,
+                              int n_kv_heads, int dh, int dv, int R, const float* cos_sin, int max_pos,
+                              const int32_t* tok_slot, const int32_t* tok_pos, const int32_t* page_table, int max_pages,
+                              int page_tokens, void* k_cache, void* v_cache, int T_tokens, int32_t* status, int half_layout,
+                              cudaStream_t stream) {
+    if (T_tokens == 0) return QS_OK;
+    if (dv <= 0) dv = dh;
+    QS_REQUIRE(T_tokens > 0 && n_heads > 0 && n_kv_heads >= 0 && dh > 0 && q && wq, "norm_rope_store: bad sizes");
+    QS_REQUIRE(n_kv_heads == 0 || (k && v && wk && k_cache && v_cache && page_table), "norm_rope_store: keys without their norm or cache");
+    QS_REQUIRE(dh % 2 == 0, "norm_rope_store: head size %d must be even", dh);
+    QS_REQUIRE(R >= 0 && R % 2 == 0 && R <= dh, "norm_rope_store: rotary width %d must be even and within the head size %d", R, dh);
+    QS_REQUIRE(page_tokens > 0 && (page_tokens & (page_tokens - 1)) == 0, "norm_rope_store: page size %d is no power of two", page_tokens);
+    int shift = 0;
+    while ((1 << shift) < page_tokens) ++shift;
+    const int work = n_heads * dh;
+    const int threads = work >= 2048 ? 256 : 128;
+    cudaError_t e;
+#define GO(T) e = qs_launch_dependent(norm_rope_store_kernel<T>, dim3(T_tokens), dim3(threads), 0, stream, (T*)q, (const T*)k, (const T*)v, \
+        (size_t)ldq, (size_t)ldk, (size_t)ldv, wq, wq_dtype, wk, wk_dtype, eps, n_heads, n_kv_heads, dh, dv, R, cos_sin, max_pos, \
+        tok_slot, tok_pos, page_table, max_pages, shift, (T*)k_cache, (T*)v_cache, status, half_layout)
+    if (dtype == QS_F32) GO(float);
+    else if (dtype == QS_BF16) GO(__nv_bfloat16);
+    else return qs_fail(QS_ERR_INVALID_INPUT, "norm_rope_store: unknown dtype %d", dtype);
+#undef GO
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "norm_rope_store: %s", cudaGetErrorString(e));
+    return qs_check_launch("norm_rope_store");
 }
 
 QS_API int qs_attention(void* out, const void* q, int dtype, long long ldo, long long ldq,

@@ -34,6 +34,9 @@ _SIGNATURES = {
     "qs_rope_store": ([c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_longlong,
                        c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                        c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_longlong, c_float, c_int, c_void_p], c_int),
+    "qs_norm_rope_store": ([c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_longlong, c_void_p, c_int, c_void_p, c_int,
+                            c_float, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                            c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p], c_int),
     "qs_attention": ([c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
                       c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
                       c_int, c_float, c_int, c_int, c_void_p, c_int, c_int, c_void_p], c_int),
@@ -294,6 +297,24 @@ def rope_store(q, k, v, n_heads, n_kv_heads, head_dim, rotary_dim, cos_sin, tok_
         page_table.shape[1] if page_table is not None else 0, page_tokens, ptr(k_cache), ptr(v_cache), T,
         ptr(status), int(bool(settled)), int(v_head_dim or head_dim), ptr(v_first),
         v_first.stride(0) if v_first is not None else 0, float(v_mix), int(bool(half_layout)), stream()))
+
+
+def norm_rope_store(q, k, v, q_weight, k_weight, eps, n_heads, n_kv_heads, head_dim, rotary_dim, cos_sin, tok_slot, tok_pos,
+                    page_table, page_tokens, k_cache, v_cache, status, v_head_dim=None, half_layout=False) -> None:
+    """One RMS norm over the whole row of q [T, n_heads * head_dim] (weight `q_weight` of that size, `eps` inside the root)
+    and one over the whole row of k, then the rotation of every head's first `rotary_dim` dims and the cache write, in
+    one kernel: q is changed in place, the cache keeps the normed and rotated k and the values v as they are (v may be
+    k: the keys as projected).  k = v = None (n_kv_heads = 0): a layer with queries only."""
+    T = q.shape[0]
+    max_pos = cos_sin.shape[0] if cos_sin is not None else 0
+    check(library().qs_norm_rope_store(
+        ptr(q), ptr(k), ptr(v), dtype_code(q), q.stride(0), k.stride(0) if k is not None else 0,
+        v.stride(0) if v is not None else 0, ptr(q_weight), _code(q_weight), ptr(k_weight), _code(k_weight), float(eps),
+        int(n_heads), int(n_kv_heads) if k is not None else 0, int(head_dim), int(v_head_dim or head_dim),
+        int(rotary_dim) if cos_sin is not None else 0, ptr(cos_sin), max_pos, _int32(tok_slot, "tok_slot"), _int32(tok_pos, "tok_pos"),
+        _int32(page_table, "page_table") if page_table is not None else None,
+        page_table.shape[1] if page_table is not None else 0, int(page_tokens), ptr(k_cache), ptr(v_cache), T, ptr(status),
+        int(bool(half_layout)), stream()))
 
 
 def attention(q, n_heads, n_kv_heads, head_dim, scale, window, tok_slot, tok_pos, page_table,

@@ -214,17 +214,35 @@ __global__ void gated_act_kernel(T* __restrict__ out, size_t ldo, const T* __res
 
 // The clamped gated unit of two halves [a | b]: g = min(a, limit), u = clamp(b, -limit, limit),
 // out = g * sigmoid(alpha * g) * (u + shift); 32-bit arithmetic, rounded once.  limit <= 0: no clamp.
-template <typename T>
+__device__ __forceinline__ float clamped_glu(float g, float u, float limit, float alpha, float shift) {
+    if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+    return g * sigmoid_f32(alpha * g) * (u + shift);
+}
+
+// VEC (bfloat16, F a multiple of 8, 16-byte aligned rows): eight columns per thread as one 16-byte piece of each half.
+template <typename T, bool VEC>
 __global__ void clamped_glu_kernel(T* __restrict__ out, size_t ldo, const T* __restrict__ ab, size_t ldi, int F, float limit,
                                    float alpha, float shift) {
     grid_dep_launch();
     grid_dep_wait();
     const size_t r = blockIdx.x;
-    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * (VEC ? 8 : 1);
     if (c >= F) return;
-    float g = to_f32(ab[r * ldi + c]), u = to_f32(ab[r * ldi + F + c]);
-    if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
-    out[r * ldo + c] = from_f32<T>(g * sigmoid_f32(alpha * g) * (u + shift));
+    if (VEC) {
+        const uint4 a = *reinterpret_cast<const uint4*>(ab + r * ldi + c), b = *reinterpret_cast<const uint4*>(ab + r * ldi + F + c);
+        const uint32_t au[4] = {a.x, a.y, a.z, a.w}, bu[4] = {b.x, b.y, b.z, b.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float a0 = __uint_as_float(au[j] << 16), a1 = __uint_as_float(au[j] & 0xffff0000u);
+            const float b0 = __uint_as_float(bu[j] << 16), b1 = __uint_as_float(bu[j] & 0xffff0000u);
+            const __nv_bfloat162 p = __floats2bfloat162_rn(clamped_glu(a0, b0, limit, alpha, shift), clamped_glu(a1, b1, limit, alpha, shift));
+            o[j] = *reinterpret_cast<const uint32_t*>(&p);
+        }
+        *reinterpret_cast<uint4*>(out + r * ldo + c) = make_uint4(o[0], o[1], o[2], o[3]);
+    } else {
+        out[r * ldo + c] = from_f32<T>(clamped_glu(to_f32(ab[r * ldi + c]), to_f32(ab[r * ldi + F + c]), limit, alpha, shift));
+    }
 }
 
 // x <- act(x), in 32-bit, rounded once: for activations that the matrix products' epilogues do not offer.
@@ -387,17 +405,25 @@ QS_API int qs_clamped_glu(void* out, long long ldo, const void* ab, long long ld
     if (rows == 0) return QS_OK;
     QS_REQUIRE(rows > 0 && F > 0 && ldi >= 2 * (long long)F && ldo >= F, "clamped_glu: bad sizes rows=%d F=%d", rows, F);
     typedef __nv_bfloat16 bf16;
-    const int threads = F >= 256 ? 256 : 64;
-    const int by = (F + threads - 1) / threads;
-    QS_REQUIRE(by <= 65535, "clamped_glu: %d columns exceed the grid", F);
     cudaError_t e;
-    if (dtype == QS_F32)
-        e = qs_launch_dependent(clamped_glu_kernel<float>, dim3(rows, by), dim3(threads), 0, stream, (float*)out, (size_t)ldo,
-                                (const float*)ab, (size_t)ldi, F, limit, alpha, shift);
-    else if (dtype == QS_BF16)
-        e = qs_launch_dependent(clamped_glu_kernel<bf16>, dim3(rows, by), dim3(threads), 0, stream, (bf16*)out, (size_t)ldo,
+    if (dtype == QS_BF16 && F % 8 == 0 && ldi % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)ab % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+        const int threads = F >= 2048 ? 256 : 64;
+        const int by = (F / 8 + threads - 1) / threads;
+        QS_REQUIRE(by <= 65535, "clamped_glu: %d columns exceed the grid", F);
+        e = qs_launch_dependent(clamped_glu_kernel<bf16, true>, dim3(rows, by), dim3(threads), 0, stream, (bf16*)out, (size_t)ldo,
                                 (const bf16*)ab, (size_t)ldi, F, limit, alpha, shift);
-    else return qs_fail(QS_ERR_INVALID_INPUT, "clamped_glu: unknown dtype %d", dtype);
+    } else {
+        const int threads = F >= 256 ? 256 : 64;
+        const int by = (F + threads - 1) / threads;
+        QS_REQUIRE(by <= 65535, "clamped_glu: %d columns exceed the grid", F);
+        if (dtype == QS_F32)
+            e = qs_launch_dependent(clamped_glu_kernel<float, false>, dim3(rows, by), dim3(threads), 0, stream, (float*)out, (size_t)ldo,
+                                    (const float*)ab, (size_t)ldi, F, limit, alpha, shift);
+        else if (dtype == QS_BF16)
+            e = qs_launch_dependent(clamped_glu_kernel<bf16, false>, dim3(rows, by), dim3(threads), 0, stream, (bf16*)out, (size_t)ldo,
+                                    (const bf16*)ab, (size_t)ldi, F, limit, alpha, shift);
+        else return qs_fail(QS_ERR_INVALID_INPUT, "clamped_glu: unknown dtype %d", dtype);
+    }
     if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "clamped_glu: %s", cudaGetErrorString(e));
     return qs_check_launch("clamped_glu");
 }

@@ -2,7 +2,9 @@
 Lutelorn adds, each against its roofline (`bench.py --design lutelorn`); the same for a Fofinex model beside a
 Lutelorn model, the library's closest design (a 32-bit stream, matrix-state mixers among attention layers), with
 the kernels that Fofinex adds (`bench.py --design fofinex`); and for a Sefuvik model beside a Lutelorn model
-(`bench.py --design sefuvik`).
+(`bench.py --design sefuvik`); and for a Nutatar model beside a Fofinex model, the library's closest design (attention
+through a latent, routed experts, a matrix-state mixer, branches normed on their way into a 32-bit stream)
+(`bench.py --design nutatar`).
 
 Sizes resemble a real model's layers: a width, heads of 128 (attention: a quarter as many key heads), a gated
 feed-forward of 8/3 width on every layer, the mixers in the order lightning, attention, lightning, wkv; the
@@ -84,6 +86,32 @@ def sefuvik_config(width: int, layers: int) -> dict:
     order = ["retention", "parallel", "retention", "attention"]
     return {"architecture": "Sefuvik", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-5}, "streams": 4,
             "layers": [kinds[order[i % 4]] for i in range(layers)], "max_positions": 8192}
+
+
+def nutatar_config(width: int, layers: int) -> dict:
+    """Heads of 128; mixers in the order latent attention (a latent of 192 + 64 rotated dims, queries through 3/4 width),
+    windowed attention (a quarter as many key heads, a window of 1,024), gated linear attention (keys of 64, values of
+    128, a bottleneck of 64), latent attention that reads the first one's latents; feed-forwards in turn dense (4 width,
+    ungated: as many weights as Fofinex's gated one of 8/3) and 16 gated experts of 1/3 width, 4 per token out of the best
+    2 of 4 groups, beside a shared one of 1/2 width."""
+    heads = width // 128
+    dense = {"kind": "dense", "ff": 4 * width}
+    routed = {"kind": "moe", "expert": {"ff": (width // 3 + 63) // 64 * 64, "limit": 7.0}, "shared": {"ff": width // 2, "limit": 7.0},
+              "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 2}}}
+    latent = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": width * 3 // 4, "kv_rank": 192, "scale": 192 ** -0.5,
+              "rot": {"dims": 64, "base": 10000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    windowed = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024},
+                "rot": {"dims": 64, "base": 10000.0}}
+    linear = {"heads": heads, "dim": 64, "vdim": 128, "tau": 16.0, "decay_rank": 64}
+    out = []
+    for i in range(layers):
+        kind = ("latent_attention", "attention", "gla", "latent_attention")[i % 4]
+        mixer = dict({"latent_attention": latent, "attention": windowed, "gla": linear}[kind])
+        if i % 4 == 3:
+            mixer["kv_from"] = i - 3                    # every second latent layer reads the latents of the one before
+        out.append({"type": kind, "mixer": mixer, "mlp": dense if i % 2 == 0 else routed})
+    return {"architecture": "Nutatar", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0}, "layers": out,
+            "max_positions": 8192}
 
 
 def gptj_config(width: int, layers: int) -> dict:
@@ -513,6 +541,189 @@ def kernel_table_sefuvik(torch, np, pk, width=2048, T=4096, batch=32, ctx=2048):
     return rows
 
 
+def kernel_table_nutatar(torch, np, pk, width=2048, T=4096, batch=32, ctx=2048):
+    """The kernels (and kernel options) that Nutatar adds, each by itself beside the like kernel of the Fofinex or Lutelorn
+    parts: milliseconds and the fraction of its roofline."""
+    from .csrc import attention_bf16, ops
+    from .parts.recurrent import CHUNK_TOKENS
+    from .parts.rotary import _table
+    t = Timer(torch)
+    bf = torch.bfloat16
+    dev = "cuda"
+    H, d = width // 128, 128
+    G = max(1, H // 4)
+    hbm, tens = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    fp32 = 2.0 * FP32_LANES_PER_SM * SMS * pk.get("sm_max_mhz", 1965.0) * 1e6
+    rows = []
+
+    def add(name, like, ms, nbytes=0, flops=0, bound="hbm"):
+        peak = {"hbm": hbm, "tensor": tens, "fp32": fp32}[bound]
+        done = (nbytes if bound == "hbm" else flops) / (ms * 1e-3)
+        rows.append({"kernel": name, "like": like, "ms": round(ms, 4), "bound": bound, "frac": round(done / peak, 4)})
+
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=dev)          # noqa: E731
+    # the stream: a normed branch joins it and the next sublayer reads it as it is, in one pass
+    for n_rows, tag in ((T, "prompt"), (batch, "decode")):
+        x, y = torch.randn(n_rows, width, device=dev), torch.randn(n_rows, width, device=dev)
+        w = torch.randn(width, device=dev, dtype=bf)
+        add(f"branch norm + update + read {tag}", "branch norm + update + norm",
+            t.kernel(lambda: ops.branch_norm(x, None, 1e-5, False, out_dtype=bf, branch=y, branch_weight=w)), n_rows * width * 14)
+        add(f"branch norm + update + norm {tag} (Fofinex)", "",
+            t.kernel(lambda: ops.branch_norm(x, w, 1e-5, True, out_dtype=bf, branch=y, branch_weight=w)), n_rows * width * 14)
+        F = (width // 3 + 63) // 64 * 64
+        ab = torch.randn(n_rows * 4, 2 * F, device=dev, dtype=bf)           # four experts' rows per token
+        add(f"clamped gated unit {tag}", "gated activation", t.kernel(lambda: ops.clamped_glu(ab, 7.0)), ab.numel() * 3)
+        ab2 = torch.randn(n_rows, 2 * ((width * 8 // 3 + 255) // 256 * 256), device=dev, dtype=bf)
+        add(f"gated activation {tag} (Lutelorn)", "", t.kernel(lambda: ops.gated_act(ab2, "silu")), ab2.numel() * 3)
+        o, g = torch.randn(n_rows, H * d, device=dev, dtype=bf), torch.randn(n_rows, H, device=dev, dtype=bf)
+        add(f"gate per head {tag}", "gated group norm", t.kernel(lambda: ops.gated_group_norm(o, 0, None, g, "sigmoid", 0.0, bf, gate_span=d)),
+            n_rows * H * d * 4)
+        og, gg, wn = torch.randn(n_rows, width, device=dev), torch.randn(n_rows, width, device=dev, dtype=bf), torch.randn(width, device=dev, dtype=bf)
+        add(f"gated group norm {tag} (Lutelorn)", "", t.kernel(lambda: ops.gated_group_norm(og, width, wn, gg, "sigmoid", 1e-6, bf)),
+            n_rows * width * 8)
+    # gated linear attention: keys of 64, values of 128, a decay per token and key channel taken from its logits in the walk
+    dk, dv = 64, 128
+    n_chunks = T // CHUNK_TOKENS
+    chunks = (i32(list(range(0, T + 1, CHUNK_TOKENS))), i32(list(range(n_chunks))), i32([0, n_chunks]), n_chunks)
+    one_start, one_slot = i32([0, T]), i32([0])
+    dec_start, dec_slot = i32(list(range(batch + 1))), i32(list(range(batch)))
+    q, k = (torch.randn(T, H * dk, device=dev, dtype=bf) for _ in range(2))
+    v = torch.randn(T, H * dv, device=dev, dtype=bf)
+    z = torch.randn(T, H * dk, device=dev) + 4.0
+    state = torch.zeros(batch, H, dv, dk, device=dev)
+    ms = t.kernel(lambda: ops.state_scan("gla", q, k, v, state, one_start, one_slot, 1, H, dk, dv, decay_logits=z, decay_power=1 / 16,
+                                         q_scale=0.125, chunks=chunks))
+    add(f"state scan gla prompt {T} (4 kernels)", "state scan gated prompt", ms, flops=6.0 * T * H * dk * dv, bound="fp32")
+    ms = t.kernel(lambda: ops.state_scan("gla", q[:batch], k[:batch], v[:batch], state, dec_start, dec_slot, batch, H, dk, dv,
+                                         decay_logits=z[:batch], decay_power=1 / 16, q_scale=0.125))
+    add(f"state scan gla decode {batch}", "state scan gated decode", ms, 2 * state.numel() * 4)
+    raw = torch.randn(T, 2 * H, device=dev)
+    m_state = torch.zeros(batch, H, device=dev)
+    a, b, _ = ops.mlstm_gates(raw, 15.0, m_state, one_start, one_slot, 1, H)
+    st1 = torch.zeros(batch, H, dv + 1, dk, device=dev)
+    ms = t.kernel(lambda: ops.state_scan("gated", q, k, v, st1, one_start, one_slot, 1, H, dk, dv + 1, token_decay=a, token_weight=b,
+                                         q_scale=0.125, chunks=chunks))
+    add(f"state scan gated prompt {T} (Fofinex)", "", ms, flops=6.0 * T * H * dk * (dv + 1), bound="fp32")
+    ms = t.kernel(lambda: ops.state_scan("gated", q[:batch], k[:batch], v[:batch], st1, dec_start, dec_slot, batch, H, dk, dv + 1,
+                                         token_decay=a[:batch], token_weight=b[:batch], q_scale=0.125))
+    add(f"state scan gated decode {batch} (Fofinex)", "", ms, 2 * st1.numel() * 4)
+    # windowed attention: one norm over the whole q and k, rotation and cache write, then a window of 1,024 with a sink
+    n_pages = batch * ctx // 64
+    table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(batch, ctx // 64)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    tl = min(T, ctx)
+    dslot, dpos = i32(list(range(batch))), i32([ctx - 1] * batch)
+    tiles = torch.tensor([(s0, min(128, tl - s0), s0, 0) for s0 in range(0, tl, 128)][::-1], dtype=torch.int32, device=dev)
+    kg, vg = (torch.randn(n_pages, G, 64, d, device=dev, dtype=bf) for _ in range(2))
+    window = 1024
+    sink = torch.zeros(H, device=dev)
+    rope = _table(64, 10000.0, 8192, dev)
+    wq, wk = torch.randn(H * d, device=dev, dtype=bf), torch.randn(G * d, device=dev, dtype=bf)
+    for n_rows, tag, slot, pos in ((tl, "prompt", i32([0] * tl), i32(list(range(tl)))), (batch, "decode", dslot, dpos)):
+        qk = torch.randn(n_rows, (H + G) * d, device=dev, dtype=bf)
+
+        def prepare():
+            qn = ops.rmsnorm(qk[:, :H * d], wq, 1e-5, out_dtype=bf)
+            kn = ops.rmsnorm(qk[:, H * d:], wk, 1e-5, out_dtype=bf)
+            ops.rope_store(qn, kn, qk[:, H * d:], H, G, d, 64, rope, slot, pos, table, 64, kg, vg, status, settled=True, half_layout=True)
+        add(f"norms of q and k, rotation, cache write {tag} (3 kernels)", "rotation and cache write",
+            t.kernel(prepare), n_rows * ((H + G) * d * 4 + H * d * 4 + G * d * 6))
+        qs_, ks_, vs_ = (torch.randn(n_rows, n * d, device=dev, dtype=bf) for n in (H, G, G))
+        add(f"rotation and cache write {tag} (Lutelorn)", "",
+            t.kernel(lambda: ops.rope_store(qs_, ks_, vs_, H, G, d, 64, rope, slot, pos, table, 64, kg, vg, status, settled=True)),
+            n_rows * (H * d * 4 + G * d * 8))
+    qw = torch.randn(tl, H * d, device=dev, dtype=bf)
+    seen = sum(min(p + 1, window) for p in range(tl))
+    ms = t.kernel(lambda: attention_bf16.prefill(qw, H, G, d, d ** -0.5, window, tiles, table, 64, kg, vg, status, sink=sink))
+    add(f"attention in a window of {window} with a sink, prompt {tl}", "attention prompt", ms, flops=4.0 * H * d * seen, bound="tensor")
+    qd = qw[:batch].contiguous()
+    ms = t.kernel(lambda: attention_bf16.decode(qd, H, G, d, d ** -0.5, window, dslot, dpos, table, 64, kg, vg, ctx, status, sink=sink))
+    add(f"attention in a window of {window} with a sink, decode {batch} x {ctx}", "attention decode", ms, batch * window * G * d * 4)
+    ms = t.kernel(lambda: attention_bf16.prefill(qw, H, G, d, d ** -0.5, 0, tiles, table, 64, kg, vg, status))
+    add(f"attention prompt {tl}, {G} key heads (Lutelorn's sizes)", "", ms, flops=4.0 * H * d * tl * tl / 2, bound="tensor")
+    ms = t.kernel(lambda: attention_bf16.decode(qd, H, G, d, d ** -0.5, 0, dslot, dpos, table, 64, kg, vg, ctx, status))
+    add(f"attention decode {batch} x {ctx}, {G} key heads (Lutelorn's sizes)", "", ms, batch * ctx * G * d * 4)
+    # the latent with a sink per head: Fofinex's kernels with the sink's term (and the rotation by neighbours)
+    r, dr, dn, rq = 192, 64, 128, width * 3 // 4
+    from .parts.rotary import scaled_frequencies
+    f, mag = scaled_frequencies(dr, 10000.0, dict(factor=4.0, original=4096, fast=32.0, slow=1.0))
+    f = f.to(dev)
+    kc = torch.randn(n_pages, 1, 64, r + dr, device=dev, dtype=bf)
+    vc = torch.randn(n_pages, 1, 64, r, device=dev, dtype=bf)
+    dd = torch.randn(T, rq + r + dr, device=dev, dtype=bf)
+    wql, wkv = torch.randn(rq, device=dev, dtype=bf), torch.randn(r, device=dev, dtype=bf)
+    for n_rows, tag, slot, pos in ((tl, "prompt", i32([0] * tl), i32(list(range(tl)))), (batch, "decode", dslot, dpos)):
+        for inter, who in ((True, ""), (False, " (Fofinex)")):
+            add(f"latent prepare {tag}{who}", "" if who else "latent prepare",
+                t.kernel(lambda: ops.latent_prepare(dd[:n_rows, :rq], wql, rq, dd[:n_rows, rq:], wkv, r, dr, dr, f, mag, 1e-5, slot, pos,
+                                                    table, 64, kc, vc, status, interleaved=inter)), n_rows * (2 * rq + 3 * r + 2 * dr) * 2)
+    qa = torch.randn(tl, H * (r + dr), device=dev, dtype=bf)
+    sinks = torch.randn(H, device=dev)
+    for sk, who in ((sinks, ""), (None, " (Fofinex)")):
+        ms = t.kernel(lambda: attention_bf16.prefill(qa, H, 1, r + dr, 0.07, 0, tiles, table, 64, kc, vc, status, v_head_dim=r, sink=sk))
+        add(f"latent attention prompt {tl}{who}", "" if who else "latent attention prompt", ms, flops=2.0 * H * (2 * r + dr) * tl * tl / 2, bound="tensor")
+        qad = qa[:batch].contiguous()
+        ms = t.kernel(lambda: attention_bf16.decode(qad, H, 1, r + dr, 0.07, 0, dslot, dpos, table, 64, kc, vc, ctx, status, v_head_dim=r, sink=sk))
+        add(f"latent attention decode {batch} x {ctx}{who}", "" if who else "latent attention decode", ms, batch * ctx * (2 * r + dr) * 2)
+    # routed experts: the router's choice (softmax, group maxima); gated experts through the routing table and ordered by expert
+    E, top, F = 16, 4, (width // 3 + 63) // 64 * 64
+    zr = torch.randn(T, E + 1, device=dev)
+    corr = torch.randn(E, device=dev) * 0.1
+    add(f"router choice prompt {T}", "router choice", t.kernel(lambda: ops.moe_route(zr, None, E, top, 4, 2, 1.0, scores="softmax", group_score="max")),
+        T * (E + 1 + 2 * top) * 4)
+    add(f"router choice prompt {T} (Fofinex)", "", t.kernel(lambda: ops.moe_route(zr, corr, E, top, 4, 2, 2.5, E)), T * (E + 1 + 2 * top + 1) * 4)
+    idx, wts, _ = ops.moe_route(zr, None, E, top, 4, 2, 1.0, scores="softmax", group_score="max")
+    w_gu = torch.randn(E, 2 * F, width, device=dev, dtype=bf) * 0.02
+    w_up, w_down = torch.randn(E, F, width, device=dev, dtype=bf) * 0.02, torch.randn(E, width, F, device=dev, dtype=bf) * 0.02
+    h = torch.randn(T, width, device=dev, dtype=bf)
+    slot_all = i32([0] * T)
+    glu = (7.0, 1.702, 1.0)
+    for nb in (8, batch):
+        used = len(set(idx[:nb].flatten().tolist()))
+        ix, wt = idx[:nb].contiguous(), wts[:nb].contiguous()
+        ms = t.kernel(lambda: ops.moe_experts_indirect(h[:nb], w_gu, w_down, ix, wt, slot_all[:nb], None, glu=glu))
+        add(f"gated experts through the routing table, {nb} tokens ({used} experts read; 3 kernels)", "experts through the routing table", ms,
+            used * 3 * F * width * 2)
+        ms = t.kernel(lambda: ops.moe_experts_indirect(h[:nb], w_up, w_down, ix, wt, slot_all[:nb], "relu2"))
+        add(f"experts through the routing table, {nb} tokens (Fofinex; 2 kernels)", "", ms, used * 2 * F * width * 2)
+
+    def grouped(gated):
+        offsets, place_token, pair_place = ops.moe_sort(idx, E)
+        rows_ = ops.gather_rows(h, place_token)
+        yy = torch.empty((rows_.shape[0], width), dtype=torch.float32, device=dev)
+        hid = torch.empty((rows_.shape[0], 2 * F if gated else F), dtype=bf, device=dev)
+        bounds = offsets.tolist()
+        ops.expert_products(hid, rows_, w_gu if gated else w_up, bounds)
+        hid = ops.clamped_glu(hid, *glu) if gated else ops.activate(hid, "relu2")
+        ops.expert_products(yy, hid, w_down, bounds)
+        return ops.moe_combine(yy, pair_place, wts, slot_all)
+    add(f"gated experts ordered by expert, {T} tokens (sort, gather, {2 * E} products, gated unit, combine)", "experts ordered by expert",
+        t.kernel(lambda: grouped(True), repeats=5), flops=6.0 * T * top * F * width, bound="tensor")
+    add(f"experts ordered by expert, {T} tokens (Fofinex)", "", t.kernel(lambda: grouped(False), repeats=5), flops=4.0 * T * top * F * width, bound="tensor")
+    return rows
+
+
+def run_nutatar(args, pk) -> int:
+    import numpy as np
+    import torch
+    import qstream_b200 as qs
+    out = {"impl": "ours", "design": "nutatar", "beside": "fofinex", "dtype": "bf16", "data": "synthetic token ids, random weights",
+           "peaks": {k: pk[k] for k in ("hbm_gbs", "bf16_tflops", "source")}, "sizes": {}}
+    for name, size in SIZES.items():
+        entry = {}
+        for which, cfg in (("nutatar", nutatar_config(**size)), ("fofinex", fofinex_config(**size))):
+            model = qs.CausalLM.random(qs.config_from_dict(cfg), seed=0, dtype="bfloat16", device="cuda:0")
+            r = model_throughput(qs, torch, np, model, VOCAB, 2048, 8, 1024, min(args.steps, 32), max(3, min(args.warmup, 4)))
+            r["weights_mb"] = round(model.weight_bytes / 2**20, 1)
+            entry[which] = r
+            del model
+            torch.cuda.empty_cache()
+        out["sizes"][name] = entry
+    out["kernels"] = kernel_table_nutatar(torch, np, pk)
+    print(json.dumps(out))
+    return 0
+
+
 def run_fofinex(args, pk) -> int:
     import numpy as np
     import torch
@@ -560,6 +771,8 @@ def run(args, pk) -> int:
         return run_fofinex(args, pk)
     if getattr(args, "design", "") == "sefuvik":
         return run_sefuvik(args, pk)
+    if getattr(args, "design", "") == "nutatar":
+        return run_nutatar(args, pk)
     import numpy as np
     import torch
     import qstream_b200 as qs

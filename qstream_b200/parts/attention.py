@@ -146,15 +146,26 @@ class Attention(Mixer):
         hq, hkv, hv = s.n_heads * self.maps * s.head_dim, s.n_kv_heads * self.maps * s.head_dim, s.n_kv_heads * s.value_dim
         qkv = linear(h, self.w_qkv, self.b_qkv)
         q = qkv[:, :hq]
-        if self.qk_norm:                                # one norm over all heads' rows at once, statistics in 32-bit
+        table = getattr(self.position, "fused_table", None) if self.position is not None else None
+        # the norms over the whole q and k, the rotation and the cache write as one kernel (a rotation that offers no
+        # table of angles: norms by themselves, then the rotation's own way)
+        fused_norm = bool(self.qk_norm) and (self.position is None or table is not None) and self.maps == 1 and not s.value_mix
+        if self.qk_norm and not fused_norm:             # one norm over all heads' rows at once, statistics in 32-bit
             q = ops.rmsnorm(q, self.q_norm, float(s.eps), out_dtype=q.dtype)
         if s.gate and out is not None:
             raise QStreamError(QsError.INVALID_INPUT, "attention: a gated mixer writes its own output")
-        table = getattr(self.position, "fused_table", None) if self.position is not None else None
         half = bool(getattr(self.position, "half_layout", False))
         if self.maps > 1 and self.position is not None:
             raise QStreamError(QsError.UNSUPPORTED_ARCH, "attention: several maps per head with a rotation")
-        if s.shares_cache:
+        if fused_norm:
+            shares = s.shares_cache
+            k = None if shares else qkv[:, hq:hq + hkv]
+            v = None if shares else (k if self.values_from_keys else qkv[:, hq + hkv:hq + hkv + hv])
+            ops.norm_rope_store(q, k, v, self.q_norm, self.k_norm, float(s.eps), s.n_heads, s.n_kv_heads, s.head_dim,
+                                getattr(self.position, "rotary_dim", 0), table, b.tok_slot, b.tok_pos, view.page_table,
+                                view.page_tokens, None if shares else view.k, None if shares else view.v, step.status,
+                                v_head_dim=s.value_dim, half_layout=half)
+        elif s.shares_cache:
             if self.position is not None:
                 if table is None:
                     self.position.apply(q, None, step, s.n_heads, s.n_kv_heads, s.head_dim)

@@ -196,3 +196,38 @@ def test_the_latent_s_rotation_by_neighbours(dims, rot_dim, scaling):
     got = q_abs.cpu().numpy().reshape(T, H, r + rot_dim)[:, :, r:]
     np.testing.assert_allclose(got, P.rotate(q[:, :, dn:], pos, dims, f, mag, True), rtol=0, atol=3e-6)
     assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("H,G,d,dims,half", [(4, 2, 16, 8, True), (1, 1, 10, 10, True), (3, 3, 6, 0, True), (6, 2, 64, 32, True), (2, 1, 8, 4, False)])
+def test_one_norm_over_all_heads_then_rotation_and_cache_write(H, G, d, dims, half):
+    """q and k normed over their whole rows, rotated by halves (or neighbours), k kept in the pages with the raw k as
+    values; positions across pages in a shuffled page order; a row of no sequence."""
+    from qstream_b200.parts.rotary import _table
+    rng = np.random.default_rng(H * d)
+    pos = np.array([0, 1, 63, 64, 65, 130, 191, 5])
+    slots = np.array([0, 0, 0, 0, 0, 0, 0, -1])
+    T = len(pos)
+    qk = r32(rng.normal(size=(T, (H + G) * d)))
+    wq, wk = r32(1 + rng.normal(0, 0.3, H * d)), r32(1 + rng.normal(0, 0.3, G * d))
+    base = 1e3
+    f = P.plain_frequencies(dims, base) if dims else np.zeros(0)
+    want_q = P.rotate(P.rms_norm(qk[:, :H * d], wq, 1e-5).reshape(T, H, d), pos, dims, f, 1.0, not half)
+    want_k = P.rotate(P.rms_norm(qk[:, H * d:], wk, 1e-5).reshape(T, G, d), pos, dims, f, 1.0, not half)
+    k_cache = torch.zeros((4, G, 64, d), dtype=torch.float32, device=DEV)
+    v_cache = torch.zeros((4, G, 64, d), dtype=torch.float32, device=DEV)
+    table = i32([[2, 0, 3, -1]])
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    x = dev(qk)
+    ops.norm_rope_store(x[:, :H * d], x[:, H * d:], x[:, H * d:], dev(wq), dev(wk), 1e-5, H, G, d, dims,
+                        _table(dims, base, 4096, DEV) if dims else None, i32(slots), i32(pos), table, 64, k_cache, v_cache, status,
+                        half_layout=half)
+    got = x.cpu().numpy()
+    np.testing.assert_allclose(got[:7, :H * d].reshape(7, H, d), want_q[:7], rtol=0, atol=3e-6)
+    np.testing.assert_array_equal(got[7, :H * d], 0.0)
+    np.testing.assert_array_equal(got[:, H * d:], qk[:, H * d:].astype(np.float32))      # k itself stays as projected
+    pages = [2, 0, 3]
+    for t in range(7):
+        p = pos[t]
+        np.testing.assert_allclose(k_cache[pages[p // 64], :, p % 64].cpu().numpy(), want_k[t], rtol=0, atol=3e-6)
+        np.testing.assert_array_equal(v_cache[pages[p // 64], :, p % 64].cpu().numpy(), qk[t, H * d:].reshape(G, d).astype(np.float32))
+    assert int(status.item()) == 0
