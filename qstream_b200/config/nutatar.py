@@ -80,8 +80,17 @@ class NutatarConfig:
         if not layers:
             raise _bad("'layers' is empty")
         emb = _get(d, "embedding", "config", dict, optional=True, default={})
+        layers = [copy.deepcopy(layer) for layer in layers]
+        for layer in layers:                            # a layer that reads another's latents may leave their sizes to that layer
+            m = layer.get("mixer") if isinstance(layer, dict) else None
+            src = m.get("kv_from") if isinstance(m, dict) else None
+            if isinstance(src, int) and not isinstance(src, bool) and 0 <= src < len(layers) and isinstance(layers[src], dict) \
+                    and isinstance(layers[src].get("mixer"), dict):
+                for key in ("kv_rank", "rot_dim", "rot"):
+                    if key not in m and key in layers[src]["mixer"]:
+                        m[key] = copy.deepcopy(layers[src]["mixer"][key])
         cfg = cls(vocab=_positive_int(d, "vocab", "config"), width=_positive_int(d, "width", "config"),
-                  layers=tuple(copy.deepcopy(layer) for layer in layers),
+                  layers=tuple(layers),
                   eps=_number(_get(d, "norm", "config", dict), "eps", "norm"),
                   embedding_scale=_number(emb, "scale", "embedding", optional=True, default=1.0),
                   max_positions=_positive_int(d, "max_positions", "config", optional=True, default=DEFAULT_MAX_POSITIONS))

@@ -573,6 +573,7 @@ def kernel_table_nutatar(torch, np, pk, width=2048, T=4096, batch=32, ctx=2048):
         F = (width // 3 + 63) // 64 * 64
         ab = torch.randn(n_rows * 4, 2 * F, device=dev, dtype=bf)           # four experts' rows per token
         add(f"clamped gated unit {tag}", "gated activation", t.kernel(lambda: ops.clamped_glu(ab, 7.0)), ab.numel() * 3)
+        add(f"gated activation {tag} at the experts' sizes", "", t.kernel(lambda: ops.gated_act(ab, "silu")), ab.numel() * 3)
         ab2 = torch.randn(n_rows, 2 * ((width * 8 // 3 + 255) // 256 * 256), device=dev, dtype=bf)
         add(f"gated activation {tag} (Lutelorn)", "", t.kernel(lambda: ops.gated_act(ab2, "silu")), ab2.numel() * 3)
         o, g = torch.randn(n_rows, H * d, device=dev, dtype=bf), torch.randn(n_rows, H, device=dev, dtype=bf)
@@ -622,12 +623,9 @@ def kernel_table_nutatar(torch, np, pk, width=2048, T=4096, batch=32, ctx=2048):
     for n_rows, tag, slot, pos in ((tl, "prompt", i32([0] * tl), i32(list(range(tl)))), (batch, "decode", dslot, dpos)):
         qk = torch.randn(n_rows, (H + G) * d, device=dev, dtype=bf)
 
-        def prepare():
-            qn = ops.rmsnorm(qk[:, :H * d], wq, 1e-5, out_dtype=bf)
-            kn = ops.rmsnorm(qk[:, H * d:], wk, 1e-5, out_dtype=bf)
-            ops.rope_store(qn, kn, qk[:, H * d:], H, G, d, 64, rope, slot, pos, table, 64, kg, vg, status, settled=True, half_layout=True)
-        add(f"norms of q and k, rotation, cache write {tag} (3 kernels)", "rotation and cache write",
-            t.kernel(prepare), n_rows * ((H + G) * d * 4 + H * d * 4 + G * d * 6))
+        add(f"norms of q and k, rotation, cache write {tag}", "rotation and cache write",
+            t.kernel(lambda: ops.norm_rope_store(qk[:, :H * d], qk[:, H * d:], qk[:, H * d:], wq, wk, 1e-5, H, G, d, 64, rope, slot, pos,
+                                                 table, 64, kg, vg, status, half_layout=True)), n_rows * (H * d * 4 + G * d * 6))
         qs_, ks_, vs_ = (torch.randn(n_rows, n * d, device=dev, dtype=bf) for n in (H, G, G))
         add(f"rotation and cache write {tag} (Lutelorn)", "",
             t.kernel(lambda: ops.rope_store(qs_, ks_, vs_, H, G, d, 64, rope, slot, pos, table, 64, kg, vg, status, settled=True)),

@@ -46,6 +46,14 @@ def test_the_schedule_and_the_parts_follow_the_layers():
     assert spec.layers[1].ffn.activation == "relu2" and spec.embedding.scale == 3.0
 
 
+def test_a_layer_that_reads_another_s_latents_may_leave_their_sizes_out():
+    cfg = copy.deepcopy(CONFIGS["A"])
+    for key in ("kv_rank", "rot_dim", "rot"):
+        del cfg["layers"][3]["mixer"][key]
+    spec = qs.config_from_dict(cfg).model_spec()
+    assert spec.layers[3].mixer == qs.config_from_dict(CONFIGS["A"]).model_spec().layers[3].mixer
+
+
 @pytest.mark.parametrize("change,needle", [
     (lambda c: c["layers"][0].update(type="conv"), "type"),
     (lambda c: c["layers"][1]["mixer"].update(kv_heads=3), "kv_heads"),
