@@ -454,6 +454,136 @@ QS_API int qs_rope_store(void* q, const void* k, const void* v, int dtype,
     return qs_check_launch("rope_store");
 }
 
+namespace {
+__device__ __forceinline__ void unpack8(const uint4 raw, float (&f)[8]) {
+    const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { f[2 * j] = __uint_as_float(u[j] << 16); f[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u); }
+}
+
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const __nv_bfloat162 p = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+        o[j] = *reinterpret_cast<const uint32_t*>(&p);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// One item of a head in 16-byte pieces: src and dst point at the head's first element, w_base is the head's first
+// weight.  Items below n_rot are rotated (HALF: dims [8 item, +8) paired with [R/2 + 8 item, +8); else the four
+// neighbouring pairs of dims [8 item, +8)), the others are the plain dims from R on.
+template <bool HALF>
+__device__ __forceinline__ void norm_rot_item(const __nv_bfloat16* src, __nv_bfloat16* dst, const void* w, int w_dtype, int w_base,
+                                              float rstd, int item, int n_rot, int R, const float* __restrict__ cs) {
+    float a[8], wa[8];
+    if (item >= n_rot) {
+        const int d0 = R + 8 * (item - n_rot);
+        unpack8(*reinterpret_cast<const uint4*>(src + d0), a);
+        load8_as_f32(w, w_dtype, w_base + d0, wa);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[i] *= rstd * wa[i];
+        *reinterpret_cast<uint4*>(dst + d0) = pack8(a);
+    } else if (HALF) {
+        const int rp = R >> 1, d0 = 8 * item;
+        float b[8], wb[8], c[16];
+        unpack8(*reinterpret_cast<const uint4*>(src + d0), a);
+        unpack8(*reinterpret_cast<const uint4*>(src + rp + d0), b);
+        load8_as_f32(w, w_dtype, w_base + d0, wa);
+        load8_as_f32(w, w_dtype, w_base + rp + d0, wb);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 x = reinterpret_cast<const float4*>(cs + 16 * item)[i];
+            c[4 * i] = x.x; c[4 * i + 1] = x.y; c[4 * i + 2] = x.z; c[4 * i + 3] = x.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float x = a[i] * rstd * wa[i], y = b[i] * rstd * wb[i];
+            a[i] = x * c[2 * i] - y * c[2 * i + 1];
+            b[i] = x * c[2 * i + 1] + y * c[2 * i];
+        }
+        *reinterpret_cast<uint4*>(dst + d0) = pack8(a);
+        *reinterpret_cast<uint4*>(dst + rp + d0) = pack8(b);
+    } else {
+        const int d0 = 8 * item;
+        unpack8(*reinterpret_cast<const uint4*>(src + d0), a);
+        load8_as_f32(w, w_dtype, w_base + d0, wa);
+        const float4 c0 = reinterpret_cast<const float4*>(cs + d0)[0], c1 = reinterpret_cast<const float4*>(cs + d0)[1];
+        const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float x = a[2 * i] * rstd * wa[2 * i], y = a[2 * i + 1] * rstd * wa[2 * i + 1];
+            a[2 * i] = x * c[2 * i] - y * c[2 * i + 1];
+            a[2 * i + 1] = x * c[2 * i + 1] + y * c[2 * i];
+        }
+        *reinterpret_cast<uint4*>(dst + d0) = pack8(a);
+    }
+}
+
+// norm_rope_store_kernel for bfloat16 in 16-byte pieces: head sizes multiples of 8, a rotated width whose items are whole
+// pieces (R a multiple of 16 by halves, of 8 by neighbours), 16-byte aligned rows.
+template <bool HALF>
+__global__ void norm_rope_store_vec_kernel(__nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                                           const __nv_bfloat16* __restrict__ v, size_t ldq, size_t ldk, size_t ldv,
+                                           const void* __restrict__ wq, int wq_dtype, const void* __restrict__ wk, int wk_dtype,
+                                           float eps, int n_heads, int n_kv_heads, int dh, int dv, int R,
+                                           const float* __restrict__ cos_sin, int max_pos, const int32_t* __restrict__ tok_slot,
+                                           const int32_t* __restrict__ tok_pos, const int32_t* __restrict__ page_table,
+                                           int max_pages, int page_shift, __nv_bfloat16* __restrict__ k_cache,
+                                           __nv_bfloat16* __restrict__ v_cache, int32_t* __restrict__ status) {
+    __shared__ float scratch[33];
+    grid_dep_launch();
+    grid_dep_wait();
+    const int t = blockIdx.x, tid = threadIdx.x, stride = blockDim.x;
+    const int slot = tok_slot[t];
+    const int nq = n_heads * dh, nk = n_kv_heads * dh;
+    __nv_bfloat16* qrow = q + (size_t)t * ldq;
+    if (slot < 0) {
+        for (int c = tid * 8; c < nq; c += stride * 8) *reinterpret_cast<uint4*>(qrow + c) = make_uint4(0u, 0u, 0u, 0u);
+        return;
+    }
+    const int pos = tok_pos[t];
+    if (R > 0 && (pos < 0 || pos >= max_pos)) { if (tid == 0) atomicExch(status, 1); return; }
+    const float* cs = R > 0 ? cos_sin + (size_t)pos * R : nullptr;
+    const __nv_bfloat16* krow = k + (size_t)t * ldk;
+    float sq = 0.f, sk = 0.f, f[8];
+    for (int c = tid * 8; c < nq; c += stride * 8) {
+        unpack8(*reinterpret_cast<const uint4*>(qrow + c), f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sq = fmaf(f[i], f[i], sq);
+    }
+    for (int c = tid * 8; c < nk; c += stride * 8) {
+        unpack8(*reinterpret_cast<const uint4*>(krow + c), f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sk = fmaf(f[i], f[i], sk);
+    }
+    const float rq = 1.0f / sqrtf(block_sum(sq, scratch) / (float)nq + eps);
+    const float rk = nk > 0 ? 1.0f / sqrtf(block_sum(sk, scratch) / (float)nk + eps) : 0.f;
+    const int n_rot = HALF ? R / 16 : R / 8, per_head = n_rot + (dh - R) / 8;
+    for (int e = tid; e < n_heads * per_head; e += stride) {
+        const int head = e / per_head, item = e - head * per_head;
+        norm_rot_item<HALF>(qrow + head * dh, qrow + head * dh, wq, wq_dtype, head * dh, rq, item, n_rot, R, cs);
+    }
+    if (n_kv_heads == 0) return;
+    const int page = page_table[(size_t)slot * max_pages + (pos >> page_shift)];
+    if (page < 0) { if (tid == 0) atomicExch(status, 2); return; }
+    const int page_tokens = 1 << page_shift;
+    const size_t in_page = (size_t)(pos & (page_tokens - 1));
+    for (int e = tid; e < n_kv_heads * per_head; e += stride) {
+        const int kvh = e / per_head, item = e - kvh * per_head;
+        norm_rot_item<HALF>(krow + kvh * dh, k_cache + (((size_t)page * n_kv_heads + kvh) * page_tokens + in_page) * dh, wk, wk_dtype,
+                            kvh * dh, rk, item, n_rot, R, cs);
+    }
+    const int dv8 = dv / 8;
+    for (int e = tid; e < n_kv_heads * dv8; e += stride) {
+        const int kvh = e / dv8, c = (e - kvh * dv8) * 8;
+        *reinterpret_cast<uint4*>(v_cache + (((size_t)page * n_kv_heads + kvh) * page_tokens + in_page) * dv + c) =
+            *reinterpret_cast<const uint4*>(v + (size_t)t * ldv + (size_t)kvh * dv + c);
+    }
+}
+}  // namespace
+
 // See norm_rope_store_kernel.  wq [n_heads * dh] and wk [n_kv_heads * dh] are the two norms' weights; n_kv_heads = 0
 // (k, v, the cache null): a layer that projects queries only.
 QS_API int qs_norm_rope_store(void* q, const void* k, const void* v, int dtype, long long ldq, long long ldk, long long ldv,
@@ -474,6 +604,21 @@ QS_API int qs_norm_rope_store(void* q, const void* k, const void* v, int dtype, 
     const int work = n_heads * dh;
     const int threads = work >= 2048 ? 256 : 128;
     cudaError_t e;
+    const bool rot_fits = R == 0 || (cos_sin && ((uintptr_t)cos_sin % 16) == 0 && (half_layout ? R % 16 == 0 : R % 8 == 0));
+    const bool aligned = dtype == QS_BF16 && dh % 8 == 0 && dv % 8 == 0 && rot_fits && ldq % 8 == 0 && ldk % 8 == 0 && ldv % 8 == 0 &&
+                         ((uintptr_t)q % 16) == 0 && ((uintptr_t)k % 16) == 0 && ((uintptr_t)v % 16) == 0 &&
+                         ((uintptr_t)k_cache % 16) == 0 && ((uintptr_t)v_cache % 16) == 0 && ((uintptr_t)wq % 32) == 0 && ((uintptr_t)wk % 32) == 0;
+    if (aligned) {
+        typedef __nv_bfloat16 bf16;
+        const int threads8 = work >= 8192 ? 256 : (work >= 2048 ? 128 : 64);
+#define GOV(HALF) e = qs_launch_dependent(norm_rope_store_vec_kernel<HALF>, dim3(T_tokens), dim3(threads8), 0, stream, (bf16*)q, (const bf16*)k, \
+        (const bf16*)v, (size_t)ldq, (size_t)ldk, (size_t)ldv, wq, wq_dtype, wk, wk_dtype, eps, n_heads, n_kv_heads, dh, dv, cos_sin ? R : 0, \
+        cos_sin, max_pos, tok_slot, tok_pos, page_table, max_pages, shift, (bf16*)k_cache, (bf16*)v_cache, status)
+        if (half_layout) GOV(true); else GOV(false);
+#undef GOV
+        if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "norm_rope_store: %s", cudaGetErrorString(e));
+        return qs_check_launch("norm_rope_store");
+    }
 #define GO(T) e = qs_launch_dependent(norm_rope_store_kernel<T>, dim3(T_tokens), dim3(threads), 0, stream, (T*)q, (const T*)k, (const T*)v, \
         (size_t)ldq, (size_t)ldk, (size_t)ldv, wq, wq_dtype, wk, wk_dtype, eps, n_heads, n_kv_heads, dh, dv, R, cos_sin, max_pos, \
         tok_slot, tok_pos, page_table, max_pages, shift, (T*)k_cache, (T*)v_cache, status, half_layout)

@@ -231,3 +231,38 @@ def test_one_norm_over_all_heads_then_rotation_and_cache_write(H, G, d, dims, ha
         np.testing.assert_allclose(k_cache[pages[p // 64], :, p % 64].cpu().numpy(), want_k[t], rtol=0, atol=3e-6)
         np.testing.assert_array_equal(v_cache[pages[p // 64], :, p % 64].cpu().numpy(), qk[t, H * d:].reshape(G, d).astype(np.float32))
     assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("H,G,d,dims,half", [(6, 2, 64, 32, True), (4, 2, 16, 16, True), (2, 1, 8, 8, False), (4, 4, 128, 64, True),
+                                             (2, 2, 32, 0, True), (3, 1, 24, 8, True)])
+def test_the_same_in_bfloat16_in_16_byte_pieces(H, G, d, dims, half):
+    """Sizes that take the kernel's 16-byte form (and one that does not), against the plain functions on the rounded
+    inputs; the result is rounded once."""
+    from qstream_b200.parts.rotary import _table
+    rng = np.random.default_rng(H * d + dims)
+    bf = torch.bfloat16
+    pos = np.array([0, 1, 63, 64, 65, 130, 191, 5])
+    slots = np.array([0, 0, 0, 0, 0, 0, 0, -1])
+    T = len(pos)
+    x = dev(rng.normal(size=(T, (H + G) * d)), bf)
+    wq, wk = dev(1 + rng.normal(0, 0.3, H * d), bf), dev(1 + rng.normal(0, 0.3, G * d), bf)
+    qk = x.double().cpu().numpy()
+    f = P.plain_frequencies(dims, 1e3) if dims else np.zeros(0)
+    want_q = P.rotate(P.rms_norm(qk[:, :H * d], wq.double().cpu().numpy(), 1e-5).reshape(T, H, d), pos, dims, f, 1.0, not half)
+    want_k = P.rotate(P.rms_norm(qk[:, H * d:], wk.double().cpu().numpy(), 1e-5).reshape(T, G, d), pos, dims, f, 1.0, not half)
+    k_cache = torch.zeros((4, G, 64, d), dtype=bf, device=DEV)
+    v_cache = torch.zeros((4, G, 64, d), dtype=bf, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.norm_rope_store(x[:, :H * d], x[:, H * d:], x[:, H * d:], wq, wk, 1e-5, H, G, d, dims,
+                        _table(dims, 1e3, 4096, DEV) if dims else None, i32(slots), i32(pos), i32([[2, 0, 3, -1]]), 64, k_cache, v_cache,
+                        status, half_layout=half)
+    got = x.double().cpu().numpy()
+    np.testing.assert_allclose(got[:7, :H * d].reshape(7, H, d), want_q[:7], rtol=2 ** -8, atol=1e-3)
+    np.testing.assert_array_equal(got[7, :H * d], 0.0)
+    np.testing.assert_array_equal(got[:, H * d:], qk[:, H * d:])
+    pages = [2, 0, 3]
+    for t in range(7):
+        p = pos[t]
+        np.testing.assert_allclose(k_cache[pages[p // 64], :, p % 64].double().cpu().numpy(), want_k[t], rtol=2 ** -8, atol=1e-3)
+        np.testing.assert_array_equal(v_cache[pages[p // 64], :, p % 64].double().cpu().numpy(), qk[t, H * d:].reshape(G, d))
+    assert int(status.item()) == 0
