@@ -89,7 +89,7 @@ CONFIG_C = model(160, 128, 1e-6, 8.0, [
 ])
 # E: wider, for long requests: three query heads to a key head, a window that spans several pages and is no multiple
 #    of one, long enough prompts for the scan's chunks, twelve experts.
-CONFIG_E = model(512, 256, 1e-6, 12.0, [
+CONFIG_E = model(400, 320, 1e-6, 12.0, [
     attention_layer(6, 2, 64, 200, 0.1, rot=(32, 1e4), mlp=moe(12, 3, 48, 1.0, groups=(3, 2), shared=(64, 1.5))),
     latent_layer(4, 48, 16, 64, 96, 112, 0.09, (16, 1e5), (16.0, 256, 24.0, 1.5), mlp=dense(320)),
     gla_layer(4, 48, 64, 8.0, mlp=dense(192)),
