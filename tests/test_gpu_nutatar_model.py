@@ -351,3 +351,37 @@ def test_a_wider_model_with_long_requests(models, dtype):
     engine.check_status()
     engine.cache.check()
     assert engine.cache.slots.n_free == engine.cache.slots.n_slots
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_far_key_among_hundreds_weighs_on_the_last_tokens(tmp_path, dtype):
+    """Latent attention alone (a layer and one that reads its latents): one early token whose embedding is six times
+    the others' gives a key that many later queries rest on (or shun).  The plain model first shows that the last
+    rows change when that token is another one; the library must agree with it 700 tokens on, in a whole prompt, in
+    portions that start behind the token's page, and token by token."""
+    cfg = CONFIGS["L"]
+    weights = make_weights(cfg, 5, gain_all=1.0 if dtype == "float32" else 0.5)
+    special = 7
+    weights["embed"][special] *= 6.0
+    folder = write_folder(tmp_path / "far", cfg, weights, dtype)
+    pcfg, w = load_plain(folder)
+    rng = np.random.default_rng(31)
+    toks = [int(t) for t in rng.integers(8, cfg["vocab"], 700)]
+    toks[2] = special
+    ref = P.forward(pcfg, w, toks)
+    other = list(toks)
+    other[2] = 9
+    moved = logits_error(P.forward(pcfg, w, other)[-100:], ref[-100:])
+    assert (moved > 0.03).sum() >= 50, (moved > 0.03).sum()
+    model = qs.load_model(folder, dtype=dtype, device="cuda")
+    engine = qs.Engine(model, max_tokens=1024, max_batch=2)
+    slot = engine.acquire()
+    got = engine.step([slot], [toks], [all_places(700)]).cpu().numpy()
+    engine.release(slot)
+    assert_close(got, ref, dtype, "whole")
+    slot = engine.acquire()
+    got = [engine.step([slot], [toks[a:b]], [all_places(b - a)]).cpu().numpy() for a, b in ((0, 70), (70, 400), (400, 640))]
+    got += [engine.step([slot], [[t]], [[0]]).cpu().numpy() for t in toks[640:]]
+    engine.release(slot)
+    assert_close(np.concatenate(got), ref, dtype, "portions, then one by one")
+    engine.check_status()
